@@ -1,0 +1,159 @@
+/*
+ * flashmask_b200.h — C ABI of libflashmask_b200.so (sm_100a only).
+ *
+ * Every entry point is `extern "C"`, takes plain pointers / integers, enqueues
+ * its work on the CUDA stream it is given and returns an int status
+ * (FM_OK == 0).  On failure nothing is launched (argument errors) or the CUDA
+ * error is captured; `fm_last_error()` returns a thread-local message.
+ * Nothing here allocates device memory unless its comment says so: outputs and
+ * workspaces are owned by the caller, and `*_workspace_bytes` says how large
+ * a workspace must be.
+ *
+ * Reference interfaces replaced (paths inside PaddlePaddle/FlashMask):
+ *   flashmask/cute/flashmask_utils.py  (prepare_block_maxmin, reduce_block_count)
+ *   flashmask/cute/ops/fwd.py          (_flash_attn_fwd)
+ *   flashmask/cute/ops/bwd.py          (_flash_attn_bwd)
+ *   flashmask/cp_balance/csrc/cp_balance_bridge.cu (fm_cpb_* C ABI)
+ */
+#ifndef FLASHMASK_B200_H_
+#define FLASHMASK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FM_OK 0
+#define FM_ERR_INVALID_ARGUMENT 1
+#define FM_ERR_UNSUPPORTED 2
+#define FM_ERR_CUDA 3
+#define FM_ERR_WORKSPACE 4
+#define FM_ERR_TIMEOUT 5
+
+#define FM_DTYPE_BF16 0
+#define FM_DTYPE_FP16 1
+
+/* Tile classes written by fm_mask_prepare (one int8 per (Q tile, K tile)). */
+#define FM_TILE_SKIP 0    /* fully masked: never computed */
+#define FM_TILE_PARTIAL 1 /* element-wise mask applied from the column bounds */
+#define FM_TILE_FULL 2    /* unmasked */
+
+/* Order of the eight per-K-tile reductions inside the `minmax` buffer:
+ * minmax[(which * BHm + bh) * nblk_pad + n], which in
+ * {LTSmax, LTSmin, LTEmax, LTEmin, UTSmax, UTSmin, UTEmax, UTEmin}.
+ * Reductions of bounds the mask does not carry are left untouched. */
+#define FM_MM_LTS_MAX 0
+#define FM_MM_LTS_MIN 1
+#define FM_MM_LTE_MAX 2
+#define FM_MM_LTE_MIN 3
+#define FM_MM_UTS_MAX 4
+#define FM_MM_UTS_MIN 5
+#define FM_MM_UTE_MAX 6
+#define FM_MM_UTE_MIN 7
+
+/* Library / build information: returns "flashmask_b200 <version> sm_100a". */
+const char* fm_version(void);
+/* Message of the last failure on the calling thread ("" when none). */
+const char* fm_last_error(void);
+
+/* Padded number of K tiles per (batch, mask head) row of `minmax`:
+ * ((ceil(Sk / tile_n) + 3) & ~3).
+ * Replaces _compute_nblock_seqlen, flashmask/cute/flashmask_utils.py:96-103. */
+int fm_mask_nblk_pad(int Sk, int tile_n);
+
+/*
+ * Mask preprocessing + tile classification.
+ *
+ *   mask       [B, Hm, Sk, ncols] int32, contiguous.  Column meaning:
+ *              ncols=1 [LTS]; causal ncols=2 [LTS,LTE]; non-causal ncols=2
+ *              [LTS,UTE]; ncols=4 [LTS,LTE,UTS,UTE].
+ *   minmax     out, int32 [8, B*Hm, nblk_pad] (see FM_MM_*); max is reduced
+ *              from 0 and min from INT_MAX; pad entries are written as 0.
+ *   valid_cnt  out (may be NULL), int32 [B, Hm, ceil(Sq/tile_m)]: number of K
+ *              tiles below the causal limit that are not fully masked.
+ *   tile_class out (may be NULL), int8 [B, Hm, ceil(Sq/tile_m), ceil(Sk/tile_n)]
+ *              FM_TILE_* including causal / ragged-edge geometry.
+ *
+ * Replaces prepare_block_maxmin + scan_max_min_kernel
+ * (flashmask/cute/flashmask_utils.py:106-190,227-282), reduce_block_count
+ * (:357-424,472-548) and the classification predicates of
+ * compute_flashmask_block_lists (:567-708) /
+ * flash_fwd_sm100.py:2297-2427 (generate_block).
+ */
+int fm_mask_prepare(const int32_t* mask, int B, int Hm, int Sq, int Sk, int ncols,
+                    int causal, int tile_m, int tile_n, int32_t* minmax,
+                    int32_t* valid_cnt, int8_t* tile_class, void* stream);
+
+/*
+ * Exact number of unmasked (query, key) pairs per (batch, mask head), from the
+ * bounds alone (element exact, O(Sk) per row).  out: int64 [B, Hm].
+ * No counterpart kernel in the reference; it is the work measure of the
+ * unmasked-FLOP throughput metric (tests/common/bench_utils.py:21-29 uses a
+ * 128x128 block density instead).
+ */
+int fm_mask_count_visible(const int32_t* mask, int B, int Hm, int Sq, int Sk,
+                          int ncols, int causal, int64_t* out, void* stream);
+
+/* Arguments shared by forward and backward.  Strides are in ELEMENTS; the
+ * innermost (head-dim) stride is 1.  Layouts follow the reference:
+ * q/o/do/dq [B,Sq,Hq,*], k/dk [B,Sk,Hkv,d], v/dv [B,Sk,Hkv,dv],
+ * lse [B,Hq,Sq] fp32 natural log (flashmask/cute/ops/fwd.py:52-110). */
+typedef struct fm_attn_args {
+  int32_t B, Sq, Sk, Hq, Hkv, Hm;
+  int32_t d, dv;      /* head dims of q/k and of v/o                        */
+  int32_t ncols;      /* 0 = no mask tensor, else 1 | 2 | 4                  */
+  int32_t causal;     /* bottom-right aligned causal triangle               */
+  int32_t dtype;      /* FM_DTYPE_*                                          */
+  int32_t mask_B;     /* batch of the mask tensor: B or 1 (broadcast)        */
+  int32_t tile_m, tile_n; /* tile shape `minmax` was prepared for            */
+  int32_t deterministic;  /* backward only                                   */
+  int32_t reserved0;
+  float softmax_scale;
+  float reserved1;
+  const void* q; const void* k; const void* v;
+  void* o; float* lse;
+  const int32_t* mask;   /* [mask_B,Hm,Sk,ncols] or NULL                    */
+  const int32_t* minmax; /* from fm_mask_prepare or NULL when ncols == 0    */
+  const float* sink;     /* [Hq] fp32 or NULL                                */
+  /* backward */
+  const void* d_o; void* dq; void* dk; void* dv_out; float* dsink;
+  void* workspace; size_t workspace_bytes;
+  int64_t q_stride[3];  /* batch, seq, head */
+  int64_t k_stride[3];
+  int64_t v_stride[3];
+  int64_t o_stride[3];
+  int64_t do_stride[3];
+  int64_t dq_stride[3];
+  int64_t dk_stride[3];
+  int64_t dv_stride[3];
+} fm_attn_args;
+
+/* Tile shape (rows of Q, columns of K per tile) the forward / backward kernel
+ * variant for (d, dv) classifies and skips on; `minmax` must be prepared with
+ * the matching tile_n.  Returns FM_ERR_UNSUPPORTED for head dims outside
+ * {<=64, <=128, 192/128, 256/256, 512/512, 576/512}
+ * (flashmask/cute/ops/_common.py:95-132). */
+int fm_fwd_tile_shape(int d, int dv, int* tile_m, int* tile_n);
+int fm_bwd_tile_shape(int d, int dv, int* tile_m, int* tile_n);
+
+/* Forward: O = softmax(QK^T*scale + M [, sink]) V and LSE.
+ * Replaces _flash_attn_fwd (flashmask/cute/ops/fwd.py:52-882) +
+ * FlashAttentionForwardSm100 (flashmask/cute/flash_fwd_sm100.py:1485-2104).
+ * Uses no workspace. */
+int fm_fwd(const fm_attn_args* args, void* stream);
+
+/* Backward: dQ, dK, dV (and dsink when sink != NULL).
+ * Replaces _flash_attn_bwd (flashmask/cute/ops/bwd.py:56-1261): preprocess
+ * (flash_bwd_preprocess.py:184-342), main (flash_bwd_sm100.py:1435-),
+ * postprocess (flash_bwd_postprocess.py:309-) and dsink
+ * (flash_bwd_sink.py:67-114).  `workspace` must hold
+ * fm_bwd_workspace_bytes(args) bytes; its contents need no initialisation. */
+size_t fm_bwd_workspace_bytes(const fm_attn_args* args);
+int fm_bwd(const fm_attn_args* args, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHMASK_B200_H_ */

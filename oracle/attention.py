@@ -1,0 +1,132 @@
+"""Dense-mask attention in fp32 on the CPU (checker, not product code).
+
+Restates tests/torch/attention_ref.py:44-226 (``attention_ref``) of the
+reference together with the bias expander
+tests/common/startend_row_indices.py:188-222, and adds what the reference's
+eager path does not return: the log-sum-exp (kernel definition
+flashmask/cute/flash_fwd_sm100.py:4873-4879) and hand-derived gradients
+(the reference obtains them with autograd over the same graph).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import numpy as np
+import torch
+
+
+def dense_bias(idx: Optional[np.ndarray], Sq: int, Sk: int, causal: bool) -> Optional[np.ndarray]:
+    """Additive bias [B, Hm, Sq, Sk] float32: 0 where visible, -inf where masked.
+
+    Vectorised restatement of startend_row_indices_to_attn_bias
+    (tests/common/startend_row_indices.py:188-222): per column j rows
+    [LTS, LTE) (or [LTS, Sq) when the mask has no LTE) are masked; causal adds
+    rows [0, j-(Sk-Sq)); non-causal adds [UTS, UTE) (or [0, UTE))."""
+    if idx is None:
+        if not causal:
+            return None
+        i = np.arange(Sq)[:, None]
+        j = np.arange(Sk)[None, :]
+        m = np.where(j > i + (Sk - Sq), -np.inf, 0.0).astype(np.float32)
+        return m[None, None]
+    a = np.asarray(idx).astype(np.int64)
+    Bm, Hm, Sk_, n = a.shape
+    assert Sk_ == Sk
+    i = np.arange(Sq, dtype=np.int64)[None, None, :, None]
+    j = np.arange(Sk, dtype=np.int64)[None, None, None, :]
+    col = [a[..., t][:, :, None, :] for t in range(n)]
+    has_end = (causal and n == 2) or ((not causal) and n == 4)
+    if has_end:
+        masked = (i >= col[0]) & (i < col[1])
+    else:
+        masked = i >= col[0]
+    if causal:
+        masked = masked | (i < np.maximum(0, j - (Sk - Sq)))
+    elif has_end:
+        masked = masked | ((i >= col[2]) & (i < col[3]))
+    else:
+        masked = masked | (i < col[1])
+    return np.where(masked, -np.inf, 0.0).astype(np.float32)
+
+
+def _expand_heads(x: torch.Tensor, H: int) -> torch.Tensor:
+    # [B, h, ...] -> [B, H, ...] repeating each head H//h times (GQA order
+    # "b h s d -> b (h g) s d", attention_ref.py:124-127)
+    h = x.shape[1]
+    if h == H:
+        return x
+    return x.repeat_interleave(H // h, dim=1)
+
+
+def attention_forward(q, k, v, idx=None, causal=False, sink=None, softmax_scale=None):
+    """Returns (out [B,Sq,Hq,dv] fp32, lse [B,Hq,Sq] fp32, P [B,Hq,Sq,Sk] fp32).
+
+    q [B,Sq,Hq,d], k [B,Sk,Hkv,d], v [B,Sk,Hkv,dv]: torch CPU tensors (any float
+    dtype; computed in fp32 as attention_ref does with upcast=True,
+    attention_ref.py:98-106).  Rows with no visible key give out = 0
+    (attention_ref.py:177-178,197) and lse = -inf (sink present: lse = sink)."""
+    q = q.to(torch.float32); k = k.to(torch.float32); v = v.to(torch.float32)
+    B, Sq, Hq, d = q.shape
+    Sk = k.shape[1]
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
+    qh = q.permute(0, 2, 1, 3)
+    kh = _expand_heads(k.permute(0, 2, 1, 3), Hq)
+    vh = _expand_heads(v.permute(0, 2, 1, 3), Hq)
+    scores = torch.matmul(qh * scale, kh.transpose(-1, -2))
+    bias = dense_bias(None if idx is None else np.asarray(idx), Sq, Sk, causal)
+    if bias is not None:
+        bt = torch.from_numpy(bias)
+        if bt.shape[0] != B:
+            bt = bt.expand(B, -1, -1, -1)
+        scores = scores + _expand_heads(bt, Hq)
+    if sink is not None:
+        s = sink.to(torch.float32).reshape(1, Hq, 1, 1).expand(B, Hq, Sq, 1)
+        full = torch.cat([scores, s], dim=-1)
+    else:
+        full = scores
+    lse = torch.logsumexp(full, dim=-1)                      # -inf for empty rows
+    safe = torch.where(torch.isinf(lse) & (lse < 0), torch.zeros_like(lse), lse)
+    P = torch.exp(scores - safe[..., None])
+    P = torch.where(torch.isinf(scores) & (scores < 0), torch.zeros_like(P), P)
+    out = torch.matmul(P, vh).permute(0, 2, 1, 3).contiguous()
+    return out, lse, P
+
+
+def attention_forward_backward(q, k, v, d_out, idx=None, causal=False, sink=None,
+                               softmax_scale=None):
+    """Forward plus gradients.  Returns dict(out, lse, dq, dk, dv, dsink).
+
+    dP = dO V^T, dS = P * (dP - rowsum(O * dO)), dQ = scale dS K,
+    dK = scale dS^T Q, dV = P^T dO, dsink[h] = -sum_{b,i} p_sink * rowsum(O*dO)
+    (flashmask/cute/flash_bwd_sm100.py:129-140, flash_bwd_sink.py:67-114); GQA
+    gradients of k/v sum over the q heads of a group."""
+    q32 = q.to(torch.float32); k32 = k.to(torch.float32); v32 = v.to(torch.float32)
+    do = d_out.to(torch.float32)
+    B, Sq, Hq, d = q32.shape
+    Sk, Hkv, dv = k32.shape[1], k32.shape[2], v32.shape[3]
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
+    out, lse, P = attention_forward(q32, k32, v32, idx, causal, sink, scale)
+    doh = do.permute(0, 2, 1, 3)
+    qh = q32.permute(0, 2, 1, 3)
+    kh = _expand_heads(k32.permute(0, 2, 1, 3), Hq)
+    vh = _expand_heads(v32.permute(0, 2, 1, 3), Hq)
+    dpsum = (out.permute(0, 2, 1, 3) * doh).sum(-1)           # [B,Hq,Sq]
+    dP = torch.matmul(doh, vh.transpose(-1, -2))
+    dS = P * (dP - dpsum[..., None])
+    dq = torch.matmul(dS, kh) * scale
+    dk_full = torch.matmul(dS.transpose(-1, -2), qh) * scale  # [B,Hq,Sk,d]
+    dv_full = torch.matmul(P.transpose(-1, -2), doh)
+    g = Hq // Hkv
+    dk = dk_full.reshape(B, Hkv, g, Sk, d).sum(2)
+    dvv = dv_full.reshape(B, Hkv, g, Sk, dv).sum(2)
+    res = dict(out=out, lse=lse,
+               dq=dq.permute(0, 2, 1, 3).contiguous(),
+               dk=dk.permute(0, 2, 1, 3).contiguous(),
+               dv=dvv.permute(0, 2, 1, 3).contiguous(), dsink=None)
+    if sink is not None:
+        s = sink.to(torch.float32).reshape(1, Hq, 1)
+        p_sink = torch.exp(s - lse)
+        p_sink = torch.where(torch.isinf(lse), torch.zeros_like(p_sink), p_sink)
+        res["dsink"] = -(p_sink * dpsum).sum(dim=(0, 2))
+    return res
