@@ -1,0 +1,311 @@
+#!/usr/bin/env python
+"""Benchmark of the FlashMask hot path: forward + backward of
+``flashmask_attention`` on a causal-document mask.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line (rank 0).  ``value`` is fwd+bwd effective TFLOP/s counting
+only unmasked (query, key) pairs, summed over all GPUs, with inputs resident in
+HBM; ``e2e`` is the same metric through the public operator with pinned HOST
+buffers (host->device and device->host copies inside the timed region);
+``roofline`` describes the dominant kernel; ``cpu_baseline`` is the CPU
+restatement of the reference's dense-mask attention timed on a bounded sample.
+``--impl reference`` times that CPU implementation alone.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+METRIC = "fwd_bwd_effective_tflops_unmasked"
+UNIT = "TFLOP/s"
+
+
+# ---------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while running."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            f = [x.strip() for x in s.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------
+# CPU baseline (the checker's dense-mask attention, fp32, all host threads)
+# ---------------------------------------------------------------------------
+def cpu_sample(w, heads: int = 4):
+    """Bounded sample of the workload for the CPU arm: batch 0, one kv head and
+    the first ``heads`` q heads of its group, the full sequence."""
+    import oracle  # CPU-baseline leg only
+    g = torch.Generator().manual_seed(w.seed)
+    q = torch.randn(1, w.Sq, heads, w.d, generator=g)
+    k = torch.randn(1, w.Sk, 1, w.d, generator=g)
+    v = torch.randn(1, w.Sk, 1, w.dv, generator=g)
+    do = torch.randn(1, w.Sq, heads, w.dv, generator=g)
+    idx = None if w.idx is None else w.idx[:1]
+    from flashmask_b200 import workloads as W
+    nvis = int(W.count_visible(idx, 1, w.Sq, w.Sk, w.causal).sum()) * heads
+    flops = 2 * nvis * (4 * w.d + 3 * w.dv)
+
+    def step():
+        return oracle.attention_forward_backward(q, k, v, do, idx, w.causal)
+    desc = f"batch 0, 1 kv head x {heads} q heads, S={w.Sq} (1/{w.B * w.Hq // heads} of the workload), fp32"
+    return step, flops, desc
+
+
+def time_cpu(step, flops, steps, warmup):
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    return flops / dt / 1e12, dt * 1e3
+
+
+# ---------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    from flashmask_b200 import workloads as W
+    name = args.workload or "causal_doc_8k_gqa"
+    w = W.make_workload(name)
+    config = {"workload": f"{name}: B={w.B} Hq={w.Hq} Hkv={w.Hkv} S={w.Sq} d={w.d} dv={w.dv} "
+                          f"causal-document mask (lognormal doc lengths), bf16, fwd+bwd",
+              "l2": "inputs+outputs (>500 MB) exceed the 126 MB L2; no flush between steps",
+              "mask_sparsity": round(w.sparsity(), 4),
+              "parallelism": "1 GPU" if world == 1 else f"{world} independent replicas"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        step, flops, desc = cpu_sample(w)
+        val, ms = time_cpu(step, flops, max(1, args.steps), max(1, args.warmup))
+        line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": config,
+                "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+                "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    import flashmask_b200 as fm
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    g = torch.Generator().manual_seed(w.seed + rank)
+    host = {
+        "q": torch.randn(w.B, w.Sq, w.Hq, w.d, generator=g).to(torch.bfloat16).pin_memory(),
+        "k": torch.randn(w.B, w.Sk, w.Hkv, w.d, generator=g).to(torch.bfloat16).pin_memory(),
+        "v": torch.randn(w.B, w.Sk, w.Hkv, w.dv, generator=g).to(torch.bfloat16).pin_memory(),
+        "do": torch.randn(w.B, w.Sq, w.Hq, w.dv, generator=g).to(torch.bfloat16).pin_memory(),
+    }
+    idx_host = torch.from_numpy(w.idx).pin_memory() if w.idx is not None else None
+    q, k, v, do = (host[n].to(dev) for n in ("q", "k", "v", "do"))
+    idx = idx_host.to(dev) if idx_host is not None else None
+    fwd_flops, bwd_flops = w.flops()
+    n_launch = {"fwd": 0, "bwd": 0}
+
+    ftm, ftn = fm.fwd_tile_shape(w.d, w.dv)
+    btm, btn = fm.bwd_tile_shape(w.d, w.dv)
+
+    def step_device():
+        # mask preprocessing is part of every step (2 launches when fwd and bwd share tile_n)
+        info_f = fm.prepare_mask(idx, w.Sq, w.causal, ftm, ftn) if idx is not None else None
+        info_b = info_f if (info_f is None or btn == ftn) else fm.prepare_mask(idx, w.Sq, w.causal, btm, btn)
+        out, lse = fm._flash_attn_fwd(q, k, v, idx, causal=w.causal, mask_info=info_f)
+        return fm._flash_attn_bwd(q, k, v, out, do, lse, idx, causal=w.causal, mask_info=info_b)
+
+    launches_per_step = (1 if idx is not None else 0) * (1 if btn == ftn else 2) + 1 + 3
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step_device()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step_device()
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    t = torch.tensor([ms_total], device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    ms_step = t.item() / args.steps
+    value = world * (fwd_flops + bwd_flops) / (ms_step * 1e-3) / 1e12
+
+    # per-kernel-group timing on the launching stream (roofline of the dominant one)
+    info_f = fm.prepare_mask(idx, w.Sq, w.causal, ftm, ftn) if idx is not None else None
+    info_b = info_f if (info_f is None or btn == ftn) else fm.prepare_mask(idx, w.Sq, w.causal, btm, btn)
+    out, lse = fm._flash_attn_fwd(q, k, v, idx, causal=w.causal, mask_info=info_f)
+
+    def timed(fn, reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+    reps = max(3, args.steps // 2)
+    ms_fwd = timed(lambda: fm._flash_attn_fwd(q, k, v, idx, causal=w.causal, mask_info=info_f), reps)
+    ms_bwd = timed(lambda: fm._flash_attn_bwd(q, k, v, out, do, lse, idx, causal=w.causal, mask_info=info_b), reps)
+    ms_prep = timed(lambda: fm.prepare_mask(idx, w.Sq, w.causal, ftm, ftn), reps) if idx is not None else 0.0
+
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak_tf = peaks.get("bf16_tflops_sustained") or 1400.0
+    peak_src = "measured (sustained cuBLAS bf16)" if peaks else "fallback"
+    dom = "bwd" if ms_bwd >= ms_fwd else "fwd"
+    dom_flops, dom_ms = (bwd_flops, ms_bwd) if dom == "bwd" else (fwd_flops, ms_fwd)
+    ach = dom_flops / (dom_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": "fm_bwd (preprocess + dK/dV + dQ kernels)" if dom == "bwd" else "fm_fwd kernel",
+                "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / peak_tf,
+                "peak_source": peak_src, "traffic": None,
+                "fwd_ms": ms_fwd, "bwd_ms": ms_bwd, "mask_prep_ms": ms_prep,
+                "fwd_tflops": fwd_flops / (ms_fwd * 1e-3) / 1e12,
+                "bwd_tflops": bwd_flops / (ms_bwd * 1e-3) / 1e12}
+
+    # end to end through the public operator with host buffers
+    def step_e2e():
+        qd = host["q"].to(dev, non_blocking=True).requires_grad_(True)
+        kd = host["k"].to(dev, non_blocking=True).requires_grad_(True)
+        vd = host["v"].to(dev, non_blocking=True).requires_grad_(True)
+        dod = host["do"].to(dev, non_blocking=True)
+        idd = idx_host.to(dev, non_blocking=True) if idx_host is not None else None
+        o = fm.flashmask_attention(qd, kd, vd, idd, causal=w.causal)
+        o.backward(dod)
+        res["out"].copy_(o.detach(), non_blocking=True)
+        res["dq"].copy_(qd.grad, non_blocking=True)
+        res["dk"].copy_(kd.grad, non_blocking=True)
+        res["dv"].copy_(vd.grad, non_blocking=True)
+    res = {"out": torch.empty_like(host["do"]).pin_memory(), "dq": torch.empty_like(host["q"]).pin_memory(),
+           "dk": torch.empty_like(host["k"]).pin_memory(), "dv": torch.empty_like(host["v"]).pin_memory()}
+    h2d = sum(t_.numel() * t_.element_size() for t_ in host.values()) + \
+        (idx_host.numel() * 4 if idx_host is not None else 0)
+    d2h = sum(t_.numel() * t_.element_size() for t_ in res.values())
+    for _ in range(2):
+        step_e2e()
+    barrier()
+    e_steps = max(3, args.steps // 2)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(e_steps):
+        step_e2e()
+    b.record()
+    barrier()
+    te = torch.tensor([a.elapsed_time(b)], device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(te, op=torch.distributed.ReduceOp.MAX)
+    e2e_val = world * (fwd_flops + bwd_flops) / (te.item() / e_steps * 1e-3) / 1e12
+
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": config, "clocks": clocks,
+            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": te.item() / e_steps},
+            "gpu_launches": launches_per_step * args.steps, "roofline": roofline,
+            "frac_of_peak_fwd_bwd": value / world / peak_tf,
+            "tokens_per_s": world * w.B * w.Sq / (ms_step * 1e-3)}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        step, flops, desc = cpu_sample(w)
+        val, ms = time_cpu(step, flops, 3, 1)
+        line["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": desc + f"; {ms:.0f} ms per fwd+bwd"}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,171 @@
+// extern "C" entry points: argument validation, kernel-variant selection,
+// workspace carving.  No allocation, no host synchronisation.
+#include <cstdarg>
+#include <cstring>
+
+#include "fm_attn_params.cuh"
+
+namespace fm {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  set_error("CUDA error %d (%s) at %s", (int)e, cudaGetErrorString(e), what);
+  return FM_ERR_CUDA;
+}
+
+// implemented in the kernel translation units
+int fwd_mma_tile_shape(int d, int dv, int* tile_m, int* tile_n);
+int fwd_mma_launch(const AttnKParams& p, int dtype, cudaStream_t s);
+int bwd_mma_tile_shape(int d, int dv, int* tile_m, int* tile_n);
+int bwd_mma_launch(const AttnKParams& p, int dtype, cudaStream_t s);
+int bwd_preprocess_launch(const AttnKParams& p, int dtype, cudaStream_t s);
+int bwd_dsink_launch(const AttnKParams& p, cudaStream_t s);
+bool fwd_sm100_supported(const fm_attn_args* a);
+int fwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s);
+bool bwd_sm100_supported(const fm_attn_args* a);
+int bwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s);
+size_t bwd_sm100_workspace_bytes(const fm_attn_args* a);
+
+static inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+static bool stride_ok(const int64_t* s) { return s[0] % 8 == 0 && s[1] % 8 == 0 && s[2] % 8 == 0; }
+
+static int validate_common(const fm_attn_args* a, const char* who) {
+  FM_REQUIRE(a != nullptr, FM_ERR_INVALID_ARGUMENT, "%s: args is NULL", who);
+  FM_REQUIRE(a->B > 0 && a->Sq > 0 && a->Sk > 0 && a->Hq > 0 && a->Hkv > 0, FM_ERR_INVALID_ARGUMENT,
+             "%s: B/Sq/Sk/Hq/Hkv must be positive", who);
+  FM_REQUIRE(a->Hq % a->Hkv == 0, FM_ERR_INVALID_ARGUMENT, "%s: Hq (%d) must be a multiple of Hkv (%d)",
+             who, a->Hq, a->Hkv);
+  FM_REQUIRE(a->d > 0 && a->dv > 0 && a->d % 8 == 0 && a->dv % 8 == 0, FM_ERR_INVALID_ARGUMENT,
+             "%s: head dims must be positive multiples of 8 (d=%d, dv=%d)", who, a->d, a->dv);
+  FM_REQUIRE(a->dtype == FM_DTYPE_BF16 || a->dtype == FM_DTYPE_FP16, FM_ERR_INVALID_ARGUMENT,
+             "%s: dtype must be FM_DTYPE_BF16 or FM_DTYPE_FP16", who);
+  FM_REQUIRE(a->q && a->k && a->v && a->o && a->lse, FM_ERR_INVALID_ARGUMENT,
+             "%s: q/k/v/o/lse must not be NULL", who);
+  FM_REQUIRE(stride_ok(a->q_stride) && stride_ok(a->k_stride) && stride_ok(a->v_stride) &&
+                 stride_ok(a->o_stride),
+             FM_ERR_INVALID_ARGUMENT, "%s: strides must be multiples of 8 elements (16-byte rows)", who);
+  FM_REQUIRE(a->ncols == 0 || a->ncols == 1 || a->ncols == 2 || a->ncols == 4, FM_ERR_INVALID_ARGUMENT,
+             "%s: ncols must be 0, 1, 2 or 4", who);
+  if (a->ncols) {
+    FM_REQUIRE(a->mask && a->minmax, FM_ERR_INVALID_ARGUMENT, "%s: mask given but mask/minmax is NULL", who);
+    FM_REQUIRE(a->Hm == 1 || a->Hm == a->Hkv || a->Hm == a->Hq, FM_ERR_INVALID_ARGUMENT,
+               "%s: mask heads (%d) must be 1, Hkv or Hq", who, a->Hm);
+    FM_REQUIRE(a->mask_B == a->B || a->mask_B == 1, FM_ERR_INVALID_ARGUMENT,
+               "%s: mask batch (%d) must be B or 1", who, a->mask_B);
+    FM_REQUIRE(!(a->ncols == 1 && !a->causal) && !(a->ncols == 4 && a->causal), FM_ERR_INVALID_ARGUMENT,
+               "%s: ncols=%d is not defined for causal=%d", who, a->ncols, a->causal);
+  }
+  return FM_OK;
+}
+
+int fill_kparams(const fm_attn_args* a, AttnKParams* p, bool backward) {
+  memset(p, 0, sizeof(*p));
+  p->q = a->q; p->k = a->k; p->v = a->v; p->o = a->o; p->lse = a->lse; p->sink = a->sink;
+  p->q_b = a->q_stride[0]; p->q_s = a->q_stride[1]; p->q_h = a->q_stride[2];
+  p->k_b = a->k_stride[0]; p->k_s = a->k_stride[1]; p->k_h = a->k_stride[2];
+  p->v_b = a->v_stride[0]; p->v_s = a->v_stride[1]; p->v_h = a->v_stride[2];
+  p->o_b = a->o_stride[0]; p->o_s = a->o_stride[1]; p->o_h = a->o_stride[2];
+  p->B = a->B; p->Sq = a->Sq; p->Sk = a->Sk; p->Hq = a->Hq; p->Hkv = a->Hkv;
+  p->d = a->d; p->dv_dim = a->dv;
+  p->Sq_r = round_up(a->Sq, 128);
+  p->scale = a->softmax_scale;
+  p->scale_log2 = a->softmax_scale * kLog2e;
+  p->md.mask = a->ncols ? a->mask : nullptr;
+  p->md.minmax = a->ncols ? a->minmax : nullptr;
+  p->md.ncols = a->ncols; p->md.causal = a->causal; p->md.Hm = a->ncols ? a->Hm : 1;
+  p->md.mask_B = a->ncols ? a->mask_B : 1;
+  p->md.nblk_pad = fm_mask_nblk_pad(a->Sk, a->tile_n > 0 ? a->tile_n : 64);
+  p->md.BHm = p->md.mask_B * p->md.Hm;
+  p->md.Sq = a->Sq; p->md.Sk = a->Sk;
+  if (backward) {
+    p->d_o = a->d_o; p->dq = a->dq; p->dk = a->dk; p->dv = a->dv_out; p->dsink = a->dsink;
+    p->do_b = a->do_stride[0]; p->do_s = a->do_stride[1]; p->do_h = a->do_stride[2];
+    p->dq_b = a->dq_stride[0]; p->dq_s = a->dq_stride[1]; p->dq_h = a->dq_stride[2];
+    p->dk_b = a->dk_stride[0]; p->dk_s = a->dk_stride[1]; p->dk_h = a->dk_stride[2];
+    p->dv_b = a->dv_stride[0]; p->dv_s = a->dv_stride[1]; p->dv_h = a->dv_stride[2];
+  }
+  return FM_OK;
+}
+
+}  // namespace fm
+
+using namespace fm;
+
+extern "C" const char* fm_version(void) { return "flashmask_b200 0.1.0 sm_100a"; }
+extern "C" const char* fm_last_error(void) { return g_err; }
+
+extern "C" int fm_fwd_tile_shape(int d, int dv, int* tile_m, int* tile_n) {
+  FM_REQUIRE(tile_m && tile_n, FM_ERR_INVALID_ARGUMENT, "fm_fwd_tile_shape: NULL output");
+  int rc = fwd_mma_tile_shape(d, dv, tile_m, tile_n);
+  if (rc != FM_OK) set_error("fm_fwd_tile_shape: unsupported head dims (d=%d, dv=%d)", d, dv);
+  return rc;
+}
+
+extern "C" int fm_bwd_tile_shape(int d, int dv, int* tile_m, int* tile_n) {
+  FM_REQUIRE(tile_m && tile_n, FM_ERR_INVALID_ARGUMENT, "fm_bwd_tile_shape: NULL output");
+  int rc = bwd_mma_tile_shape(d, dv, tile_m, tile_n);
+  if (rc != FM_OK) set_error("fm_bwd_tile_shape: unsupported head dims (d=%d, dv=%d)", d, dv);
+  return rc;
+}
+
+extern "C" int fm_fwd(const fm_attn_args* a, void* stream) {
+  int rc = validate_common(a, "fm_fwd");
+  if (rc != FM_OK) return rc;
+  int tm, tn;
+  rc = fm_fwd_tile_shape(a->d, a->dv, &tm, &tn);
+  if (rc != FM_OK) return rc;
+  FM_REQUIRE(a->ncols == 0 || a->tile_n == tn, FM_ERR_INVALID_ARGUMENT,
+             "fm_fwd: minmax was prepared for tile_n=%d, this variant needs %d", a->tile_n, tn);
+  AttnKParams p;
+  fill_kparams(a, &p, false);
+  p.md.nblk_pad = fm_mask_nblk_pad(a->Sk, tn);
+  return fwd_mma_launch(p, a->dtype, (cudaStream_t)stream);
+}
+
+extern "C" size_t fm_bwd_workspace_bytes(const fm_attn_args* a) {
+  if (!a || a->B <= 0 || a->Hq <= 0 || a->Sq <= 0) return 0;
+  const size_t rows = (size_t)a->B * a->Hq * round_up(a->Sq, 128);
+  return 2 * rows * sizeof(float);
+}
+
+extern "C" int fm_bwd(const fm_attn_args* a, void* stream) {
+  int rc = validate_common(a, "fm_bwd");
+  if (rc != FM_OK) return rc;
+  FM_REQUIRE(a->d_o && a->dq && a->dk && a->dv_out, FM_ERR_INVALID_ARGUMENT,
+             "fm_bwd: d_o/dq/dk/dv must not be NULL");
+  FM_REQUIRE(stride_ok(a->do_stride) && stride_ok(a->dq_stride) && stride_ok(a->dk_stride) &&
+                 stride_ok(a->dv_stride),
+             FM_ERR_INVALID_ARGUMENT, "fm_bwd: strides must be multiples of 8 elements");
+  FM_REQUIRE(!(a->sink && !a->dsink), FM_ERR_INVALID_ARGUMENT, "fm_bwd: sink given but dsink is NULL");
+  int tm, tn;
+  rc = fm_bwd_tile_shape(a->d, a->dv, &tm, &tn);
+  if (rc != FM_OK) return rc;
+  FM_REQUIRE(a->ncols == 0 || a->tile_n == tn, FM_ERR_INVALID_ARGUMENT,
+             "fm_bwd: minmax was prepared for tile_n=%d, this variant needs %d", a->tile_n, tn);
+  const size_t need = fm_bwd_workspace_bytes(a);
+  FM_REQUIRE(a->workspace && a->workspace_bytes >= need, FM_ERR_WORKSPACE,
+             "fm_bwd: workspace too small (%zu bytes given, %zu needed)", a->workspace_bytes, need);
+  FM_REQUIRE(((uintptr_t)a->workspace & 255) == 0, FM_ERR_WORKSPACE, "fm_bwd: workspace must be 256-byte aligned");
+  AttnKParams p;
+  fill_kparams(a, &p, true);
+  p.md.nblk_pad = fm_mask_nblk_pad(a->Sk, tn);
+  const size_t rows = (size_t)a->B * a->Hq * p.Sq_r;
+  p.dpsum = reinterpret_cast<float*>(a->workspace);
+  p.lse_log2 = p.dpsum + rows;
+  cudaStream_t s = (cudaStream_t)stream;
+  rc = bwd_preprocess_launch(p, a->dtype, s);
+  if (rc != FM_OK) return rc;
+  rc = bwd_mma_launch(p, a->dtype, s);
+  if (rc != FM_OK) return rc;
+  if (a->sink) rc = bwd_dsink_launch(p, s);
+  return rc;
+}

@@ -1,0 +1,199 @@
+// Shared device/host helpers for the flashmask_b200 kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <climits>
+#include <cstdio>
+
+#include "flashmask_b200.h"
+
+namespace fm {
+
+// ---------------------------------------------------------------------------
+// error plumbing (host)
+// ---------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define FM_CUDA_TRY(expr)                                     \
+  do {                                                        \
+    cudaError_t _e = (expr);                                  \
+    if (_e != cudaSuccess) return ::fm::cuda_fail(_e, #expr); \
+  } while (0)
+
+#define FM_REQUIRE(cond, code, ...)     \
+  do {                                  \
+    if (!(cond)) {                      \
+      ::fm::set_error(__VA_ARGS__);     \
+      return (code);                    \
+    }                                   \
+  } while (0)
+
+// ---------------------------------------------------------------------------
+// mask geometry shared by all attention kernels
+// ---------------------------------------------------------------------------
+struct MaskDesc {
+  const int32_t* mask;    // [mask_B, Hm, Sk, ncols] or nullptr
+  const int32_t* minmax;  // [8, mask_B*Hm, nblk_pad] or nullptr
+  int ncols;              // 0 | 1 | 2 | 4
+  int causal;
+  int Hm, mask_B, nblk_pad, BHm;
+  int Sq, Sk;
+};
+
+// Column bounds normalised to two masked row intervals [lts,lte) U [uts,ute).
+struct Bounds4 {
+  int lts, lte, uts, ute;
+};
+
+__device__ __forceinline__ Bounds4 load_bounds(const MaskDesc& md, const int32_t* col_ptr) {
+  // col_ptr points at the first int of column j.
+  Bounds4 b;
+  b.lts = INT_MAX; b.lte = INT_MAX; b.uts = 0; b.ute = 0;
+  if (md.ncols == 1) {
+    b.lts = col_ptr[0];
+  } else if (md.ncols == 2) {
+    int2 v = *reinterpret_cast<const int2*>(col_ptr);
+    b.lts = v.x;
+    if (md.causal) b.lte = v.y; else b.ute = v.y;
+  } else if (md.ncols == 4) {
+    int4 v = *reinterpret_cast<const int4*>(col_ptr);
+    b.lts = v.x; b.lte = v.y; b.uts = v.z; b.ute = v.w;
+  }
+  return b;
+}
+
+// Tile class of rows [ms, me) against K tile n from the per-tile reductions.
+// Predicates: skip iff every element is masked by the bounds, partial iff some
+// bound may cut through the tile; causal / ragged-edge geometry on top.
+__device__ __forceinline__ int classify_tile(const MaskDesc& md, int bh_mask, int n, int ms, int me,
+                                             int tile_n) {
+  const int ns = n * tile_n;
+  const int ne = min(ns + tile_n, md.Sk);
+  const int off = md.Sk - md.Sq;
+  bool skip = false, needs = ne < ns + tile_n;
+  if (md.causal) {
+    const bool c_empty = ns > (me - 1 + off);
+    const bool c_full = (ne - 1) <= (ms + off);
+    skip = c_empty;
+    needs = needs || (!c_empty && !c_full);
+  }
+  if (md.ncols) {
+    const int32_t* mm = md.minmax + (size_t)bh_mask * md.nblk_pad + n;
+    const size_t slot = (size_t)md.BHm * md.nblk_pad;
+    const int lts_max = mm[FM_MM_LTS_MAX * slot], lts_min = mm[FM_MM_LTS_MIN * slot];
+    bool fully, part;
+    if (md.ncols == 4) {
+      const int lte_max = mm[FM_MM_LTE_MAX * slot], lte_min = mm[FM_MM_LTE_MIN * slot];
+      const int uts_max = mm[FM_MM_UTS_MAX * slot], uts_min = mm[FM_MM_UTS_MIN * slot];
+      const int ute_max = mm[FM_MM_UTE_MAX * slot], ute_min = mm[FM_MM_UTE_MIN * slot];
+      fully = (ms >= lts_max && me <= lte_min) || (ms >= uts_max && me <= ute_min);
+      part = (ms < lte_max && me > lts_min) || (ms < ute_max && me > uts_min);
+    } else if (md.ncols == 2 && md.causal) {
+      const int lte_max = mm[FM_MM_LTE_MAX * slot], lte_min = mm[FM_MM_LTE_MIN * slot];
+      fully = ms >= lts_max && me <= lte_min;
+      part = ms < lte_max && me > lts_min;
+    } else if (md.ncols == 2) {
+      const int ute_max = mm[FM_MM_UTE_MAX * slot], ute_min = mm[FM_MM_UTE_MIN * slot];
+      fully = ms >= lts_max || me <= ute_min;
+      part = me > lts_min || ms < ute_max;
+    } else {
+      fully = ms >= lts_max;
+      part = me > lts_min;
+    }
+    skip = skip || fully;
+    needs = needs || part;
+  }
+  return skip ? FM_TILE_SKIP : (needs ? FM_TILE_PARTIAL : FM_TILE_FULL);
+}
+
+// ---------------------------------------------------------------------------
+// small PTX wrappers used by the warp-MMA kernels
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool pred) {
+  const int sz = pred ? 16 : 0;  // src-size 0 => zero fill
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(sz));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t (&r)[2], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n"
+               : "=r"(r[0]), "=r"(r[1])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n"
+               : "=r"(r[0]), "=r"(r[1])
+               : "r"(addr));
+}
+
+// D(16x8,f32) += A(16x16) * B(16x8); IS_BF16 selects bf16 / f16 operands.
+template <bool IS_BF16>
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+  if constexpr (IS_BF16) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  } else {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+}
+
+template <bool IS_BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (IS_BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Byte offset of 16-byte chunk `chunk` of row `row` in a tile whose rows hold
+// ROW_BYTES bytes (ROW_BYTES/16 a multiple of 8): XOR swizzle on the low 3 bits
+// so that ldmatrix over 8 consecutive rows is bank-conflict free.
+template <int ROW_BYTES>
+__device__ __forceinline__ uint32_t swz(int row, int chunk) {
+  return (uint32_t)row * ROW_BYTES + (uint32_t)((chunk ^ (row & 7)) << 4);
+}
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+}  // namespace fm

@@ -25,6 +25,13 @@
 extern "C" {
 #endif
 
+/* Exported symbol marker (the library is built with hidden visibility). */
+#if defined(__GNUC__)
+#define FM_API __attribute__((visibility("default")))
+#else
+#define FM_API
+#endif
+
 #define FM_OK 0
 #define FM_ERR_INVALID_ARGUMENT 1
 #define FM_ERR_UNSUPPORTED 2
@@ -54,14 +61,14 @@ extern "C" {
 #define FM_MM_UTE_MIN 7
 
 /* Library / build information: returns "flashmask_b200 <version> sm_100a". */
-const char* fm_version(void);
+FM_API const char* fm_version(void);
 /* Message of the last failure on the calling thread ("" when none). */
-const char* fm_last_error(void);
+FM_API const char* fm_last_error(void);
 
 /* Padded number of K tiles per (batch, mask head) row of `minmax`:
  * ((ceil(Sk / tile_n) + 3) & ~3).
  * Replaces _compute_nblock_seqlen, flashmask/cute/flashmask_utils.py:96-103. */
-int fm_mask_nblk_pad(int Sk, int tile_n);
+FM_API int fm_mask_nblk_pad(int Sk, int tile_n);
 
 /*
  * Mask preprocessing + tile classification.
@@ -82,7 +89,7 @@ int fm_mask_nblk_pad(int Sk, int tile_n);
  * compute_flashmask_block_lists (:567-708) /
  * flash_fwd_sm100.py:2297-2427 (generate_block).
  */
-int fm_mask_prepare(const int32_t* mask, int B, int Hm, int Sq, int Sk, int ncols,
+FM_API int fm_mask_prepare(const int32_t* mask, int B, int Hm, int Sq, int Sk, int ncols,
                     int causal, int tile_m, int tile_n, int32_t* minmax,
                     int32_t* valid_cnt, int8_t* tile_class, void* stream);
 
@@ -93,7 +100,7 @@ int fm_mask_prepare(const int32_t* mask, int B, int Hm, int Sq, int Sk, int ncol
  * unmasked-FLOP throughput metric (tests/common/bench_utils.py:21-29 uses a
  * 128x128 block density instead).
  */
-int fm_mask_count_visible(const int32_t* mask, int B, int Hm, int Sq, int Sk,
+FM_API int fm_mask_count_visible(const int32_t* mask, int B, int Hm, int Sq, int Sk,
                           int ncols, int causal, int64_t* out, void* stream);
 
 /* Arguments shared by forward and backward.  Strides are in ELEMENTS; the
@@ -135,14 +142,14 @@ typedef struct fm_attn_args {
  * the matching tile_n.  Returns FM_ERR_UNSUPPORTED for head dims outside
  * {<=64, <=128, 192/128, 256/256, 512/512, 576/512}
  * (flashmask/cute/ops/_common.py:95-132). */
-int fm_fwd_tile_shape(int d, int dv, int* tile_m, int* tile_n);
-int fm_bwd_tile_shape(int d, int dv, int* tile_m, int* tile_n);
+FM_API int fm_fwd_tile_shape(int d, int dv, int* tile_m, int* tile_n);
+FM_API int fm_bwd_tile_shape(int d, int dv, int* tile_m, int* tile_n);
 
 /* Forward: O = softmax(QK^T*scale + M [, sink]) V and LSE.
  * Replaces _flash_attn_fwd (flashmask/cute/ops/fwd.py:52-882) +
  * FlashAttentionForwardSm100 (flashmask/cute/flash_fwd_sm100.py:1485-2104).
  * Uses no workspace. */
-int fm_fwd(const fm_attn_args* args, void* stream);
+FM_API int fm_fwd(const fm_attn_args* args, void* stream);
 
 /* Backward: dQ, dK, dV (and dsink when sink != NULL).
  * Replaces _flash_attn_bwd (flashmask/cute/ops/bwd.py:56-1261): preprocess
@@ -150,8 +157,8 @@ int fm_fwd(const fm_attn_args* args, void* stream);
  * postprocess (flash_bwd_postprocess.py:309-) and dsink
  * (flash_bwd_sink.py:67-114).  `workspace` must hold
  * fm_bwd_workspace_bytes(args) bytes; its contents need no initialisation. */
-size_t fm_bwd_workspace_bytes(const fm_attn_args* args);
-int fm_bwd(const fm_attn_args* args, void* stream);
+FM_API size_t fm_bwd_workspace_bytes(const fm_attn_args* args);
+FM_API int fm_bwd(const fm_attn_args* args, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,190 @@
+"""GPU parity of forward / backward against the CPU oracle, through the public
+operator (which calls the C ABI).  Tolerance: the reference's own rule."""
+import glob
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from flashmask_b200 import workloads as W
+import flashmask_b200 as fm
+from _util import (assert_lse, assert_parity, make_inputs, naive_lowp, run_oracle, run_product)
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "attention_*.npz")))
+
+
+def _docs(rng, S, n):
+    return W.uniform_doc_lengths(rng, S, n)
+
+
+def _mask(kind, B, Sq, Sk, seed):
+    rng = np.random.default_rng(seed)
+    if kind == "none_causal":
+        return None, True
+    if kind == "none_full":
+        return None, False
+    if kind == "causal_doc":
+        m = [W.causal_document(1, Sq, Sk, _docs(rng, Sk, 5))[0] for _ in range(B)]
+        return np.concatenate(m), True
+    if kind == "bidir_doc":
+        m = [W.bidirectional_document(1, Sq, Sk, _docs(rng, Sk, 4))[0] for _ in range(B)]
+        return np.concatenate(m), False
+    if kind == "sliding_window":
+        return W.sliding_window(B, Sq, Sk, max(3, Sk // 7))
+    if kind == "share_question":
+        return W.share_question(B, Sq, Sk, Sk // 6, Sk // 12, 3)
+    if kind == "random_eviction":
+        return W.random_eviction(B, Sq, Sk, rng)
+    if kind == "four_column":
+        return W.four_column_bands(B, Sq, Sk, rng)
+    if kind == "prefix_lm":
+        third = Sk // 3
+        return W.prefix_lm_document(B, Sq, Sk, [(third // 2, third), (third // 4, third), (5, Sk - 2 * third)])
+    if kind == "cp_form":
+        return W.causal_document_noncausal_form(B, Sq, Sk, _docs(rng, Sk, 6))
+    if kind == "empty":
+        return W.empty_mask(B, Sq, Sk)
+    raise KeyError(kind)
+
+
+MASKS = ["none_causal", "none_full", "causal_doc", "bidir_doc", "sliding_window", "share_question",
+         "random_eviction", "four_column", "prefix_lm", "cp_form", "empty"]
+
+
+def _run(kind, B, Sq, Sk, Hq, Hkv, d, dv, sink=False, seed=0, dtype=torch.bfloat16, hm=1):
+    idx_np, causal = _mask(kind, B, Sq, Sk, seed)
+    if idx_np is not None and hm > 1:
+        rng = np.random.default_rng(seed + 99)
+        per = [_mask(kind, B, Sq, Sk, seed + 1 + h)[0] for h in range(hm)]
+        idx_np = np.ascontiguousarray(np.concatenate(per, axis=1))
+    q, k, v, do, s = make_inputs(B, Sq, Sk, Hq, Hkv, d, dv, seed, dtype=dtype, sink=sink)
+    idx = None if idx_np is None else torch.from_numpy(idx_np).cuda()
+    qc, kc, vc, doc = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    got = run_product(qc, kc, vc, doc, idx, causal, s)
+    ref = run_oracle(q, k, v, do, idx, causal, s)
+    lowp = naive_lowp(qc, kc, vc, doc, idx, causal, s)
+    assert_parity(got, ref, lowp, label=f"{kind}: ")
+    assert_lse(got, ref)
+    if sink:
+        err = (got["dsink"].float().cpu() - ref["dsink"]).abs().max().item()
+        scale = ref["dsink"].abs().max().item() + 1.0
+        assert err <= 1e-2 + 2 * 2 ** -8 * scale, f"dsink err {err}"
+    return got, ref
+
+
+@pytest.mark.parametrize("kind", MASKS)
+def test_masks_d128_gqa(kind):
+    _run(kind, 2, 384, 384, 4, 2, 128, 128, seed=11)
+
+
+@pytest.mark.parametrize("kind", ["causal_doc", "bidir_doc", "four_column", "none_causal"])
+def test_ragged_shapes(kind):
+    # sequence lengths that are not multiples of any tile, Sq != Sk
+    _run(kind, 1, 300, 300, 2, 2, 128, 128, seed=3)
+    if kind in ("causal_doc", "none_causal"):
+        _run(kind, 1, 203, 333, 2, 1, 64, 64, seed=4)
+
+
+@pytest.mark.parametrize("d,dv,Hq,Hkv", [(64, 64, 2, 2), (80, 80, 2, 1), (128, 128, 4, 1),
+                                         (192, 128, 4, 2), (256, 256, 2, 2), (576, 512, 2, 1),
+                                         (512, 512, 2, 1)])
+@pytest.mark.parametrize("kind", ["causal_doc", "bidir_doc"])
+def test_head_dims(kind, d, dv, Hq, Hkv):
+    _run(kind, 1, 320, 320, Hq, Hkv, d, dv, sink=True, seed=5)
+
+
+@pytest.mark.parametrize("kind", ["none_causal", "causal_doc", "random_eviction"])
+def test_sink(kind):
+    _run(kind, 2, 256, 256, 4, 2, 128, 128, sink=True, seed=7)
+
+
+def test_mask_heads_per_kv_head():
+    _run("causal_doc", 2, 256, 256, 4, 2, 128, 128, seed=8, hm=2)
+
+
+def test_fp16():
+    _run("causal_doc", 1, 256, 256, 2, 2, 128, 128, seed=9, dtype=torch.float16)
+
+
+def test_cpu_config_shape():
+    """The CPU-runnable configuration: B=1, H=2, S=1024, d=64, 4 documents."""
+    w = W.make_workload("cpu_causal_doc_1k")
+    q, k, v, do, _ = make_inputs(w.B, w.Sq, w.Sk, w.Hq, w.Hkv, w.d, w.dv, w.seed)
+    idx = torch.from_numpy(w.idx).cuda()
+    got = run_product(q.cuda(), k.cuda(), v.cuda(), do.cuda(), idx, w.causal, None)
+    ref = run_oracle(q, k, v, do, idx, w.causal, None)
+    lowp = naive_lowp(q.cuda(), k.cuda(), v.cuda(), do.cuda(), idx, w.causal, None)
+    assert_parity(got, ref, lowp)
+    assert_lse(got, ref)
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=lambda p: os.path.basename(p)[10:-4])
+def test_against_reference_golden(path):
+    """Vectors produced by the reference's own dense-mask attention (fp32).
+    Head dim 16 is padded to the 64 bucket by the kernels."""
+    z = np.load(path)
+    c = {k_: z[k_] for k_ in z.files}
+    causal = bool(c["causal"])
+    dt = torch.bfloat16
+    q, k, v, do = (torch.from_numpy(c[n]).to(dt) for n in ("q", "k", "v", "do"))
+    sink = torch.from_numpy(c["sink"]) if "sink" in c else None
+    idx = torch.from_numpy(c["idx"]).cuda() if "idx" in c else None
+    got = run_product(q.cuda(), k.cuda(), v.cuda(), do.cuda(), idx, causal, sink)
+    ref = run_oracle(q, k, v, do, idx, causal, sink)       # oracle on the bf16-rounded inputs
+    lowp = naive_lowp(q.cuda(), k.cuda(), v.cuda(), do.cuda(), idx, causal, sink)
+    assert_parity(got, ref, lowp)
+    # and against the stored reference outputs themselves (fp32 inputs there, bf16 here)
+    for n in ("out", "dq", "dk", "dv"):
+        err = (got[n].float().cpu() - torch.from_numpy(c[n])).abs().max().item()
+        assert err < 0.15, (n, err)
+
+
+def test_deterministic_bitwise():
+    idx_np, causal = _mask("causal_doc", 2, 512, 512, 21)
+    q, k, v, do, s = make_inputs(2, 512, 512, 8, 2, 128, 128, 21, sink=True)
+    idx = torch.from_numpy(idx_np).cuda()
+    a = run_product(q.cuda(), k.cuda(), v.cuda(), do.cuda(), idx, causal, s, deterministic=True)
+    for _ in range(3):
+        b = run_product(q.cuda(), k.cuda(), v.cuda(), do.cuda(), idx, causal, s, deterministic=True)
+        for n in ("out", "lse", "dq", "dk", "dv", "dsink"):
+            assert torch.equal(a[n], b[n]), n
+
+
+def test_layout_invariance():
+    """Contiguous vs permuted storage of q/k/v give bitwise equal results
+    (reference: tests/torch/test_flashmask.py:354-396)."""
+    idx_np, causal = _mask("causal_doc", 1, 256, 256, 5)
+    q, k, v, do, _ = make_inputs(1, 256, 256, 4, 2, 128, 128, 5)
+    idx = torch.from_numpy(idx_np).cuda()
+    a = run_product(q.cuda(), k.cuda(), v.cuda(), do.cuda(), idx, causal, None, deterministic=True)
+
+    def bhsd(t):  # same values, [B,H,S,D] storage viewed as [B,S,H,D]
+        return t.cuda().permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+    b = run_product(bhsd(q), bhsd(k), bhsd(v), bhsd(do), idx, causal, None, deterministic=True)
+    for n in ("out", "dq", "dk", "dv"):
+        assert torch.equal(a[n], b[n]), n
+
+
+def test_window_size_kwarg():
+    q, k, v, do, _ = make_inputs(1, 256, 256, 2, 2, 64, 64, 1)
+    out = fm.flashmask_attention(q.cuda(), k.cuda(), v.cuda(), causal=True, window_size=32)
+    idx, causal = W.sliding_window(1, 256, 256, 32)
+    ref = fm.flashmask_attention(q.cuda(), k.cuda(), v.cuda(), torch.from_numpy(idx).cuda(), causal=True)
+    assert torch.equal(out, ref)
+
+
+def test_errors():
+    q, k, v, do, _ = make_inputs(1, 64, 64, 2, 2, 64, 64, 1)
+    with pytest.raises(RuntimeError):
+        fm.flashmask_attention(q, k, v)  # CPU tensors: no fallback
+    with pytest.raises(AssertionError):
+        fm.flashmask_attention(q.cuda(), k.cuda(), v.cuda(),
+                               torch.zeros(1, 1, 64, 4, dtype=torch.int32).cuda(), causal=True)
+    with pytest.raises(NotImplementedError):
+        fm.flashmask_attention(q.cuda()[..., :40].contiguous().repeat(1, 1, 1, 8),
+                               k.cuda()[..., :40].contiguous().repeat(1, 1, 1, 8),
+                               v.cuda()[..., :40].contiguous().repeat(1, 1, 1, 8))

@@ -1,0 +1,82 @@
+"""Bit-exact parity of the mask-preprocessing / tile-classification kernels
+against the CPU restatement, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle import tiles
+import flashmask_b200 as fm
+from flashmask_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+
+def _masks(B, Sq, Sk, seed):
+    rng = np.random.default_rng(seed)
+    docs = W.uniform_doc_lengths(rng, Sk, 7)
+    yield "causal_doc", W.causal_document(B, Sq, Sk, docs)
+    yield "bidir_doc", W.bidirectional_document(B, Sq, Sk, docs)
+    yield "sliding_window", W.sliding_window(B, Sq, Sk, max(2, Sk // 9))
+    yield "share_question", W.share_question(B, Sq, Sk, max(1, Sk // 6), max(1, Sk // 12), 3)
+    yield "random_eviction", W.random_eviction(B, Sq, Sk, rng)
+    yield "four_column", W.four_column_bands(B, Sq, Sk, rng)
+    yield "cp_form", W.causal_document_noncausal_form(B, Sq, Sk, docs)
+    yield "empty", W.empty_mask(B, Sq, Sk)
+
+
+@pytest.mark.parametrize("Sq,Sk", [(1024, 1024), (300, 300), (203, 333), (4096, 4096), (1, 1), (129, 64)])
+@pytest.mark.parametrize("tile_m,tile_n", [(128, 64), (64, 64), (128, 128), (256, 128), (64, 32)])
+def test_prepare_bit_exact(Sq, Sk, tile_m, tile_n):
+    B = 2
+    for name, (idx_np, causal) in _masks(B, Sq, Sk, Sq * 7 + Sk):
+        # give the two batches different content
+        idx_np = idx_np.copy()
+        idx_np[1] = np.minimum(idx_np[1] + (idx_np.shape[2] // 5), Sq) if Sq > 8 else idx_np[1]
+        ncols = idx_np.shape[-1]
+        info = fm.prepare_mask(torch.from_numpy(idx_np).cuda(), Sq, causal, tile_m, tile_n,
+                               want_count=True, want_class=True)
+        mm = tiles.scan_max_min(idx_np, tile_n, causal)
+        got_mm = info.minmax.cpu().numpy()
+        for smax, smin in tiles.column_slots(ncols, causal):
+            assert np.array_equal(got_mm[smax], mm[smax]), (name, "max", smax)
+            assert np.array_equal(got_mm[smin], mm[smin]), (name, "min", smin)
+        cnt = tiles.valid_block_count(mm, B, 1, Sq, Sk, ncols, causal, tile_m, tile_n)
+        cls = tiles.classify_tiles(mm, B, 1, Sq, Sk, ncols, causal, tile_m, tile_n)
+        assert np.array_equal(info.valid_block_count.cpu().numpy(), cnt), name
+        assert np.array_equal(info.tile_class.cpu().numpy(), cls), name
+
+
+def test_classification_is_sound():
+    """No skipped tile holds a visible element, no FULL tile a masked one."""
+    Sq = Sk = 512
+    for name, (idx_np, causal) in _masks(1, Sq, Sk, 5):
+        info = fm.prepare_mask(torch.from_numpy(idx_np).cuda(), Sq, causal, 64, 64, want_class=True)
+        cls = info.tile_class.cpu().numpy()[0, 0]
+        vis = W.dense_visible(idx_np, Sq, causal)[0, 0].reshape(8, 64, 8, 64)
+        assert not (vis.any(axis=(1, 3)) & (cls == 0)).any(), name
+        assert not ((~vis.all(axis=(1, 3))) & (cls == 2)).any(), name
+
+
+def test_count_visible_exact():
+    for Sq, Sk in [(512, 512), (203, 333), (333, 203)]:
+        for name, (idx_np, causal) in _masks(2, Sq, Sk, 3):
+            got = fm.count_visible(torch.from_numpy(idx_np).cuda(), Sq, causal).cpu().numpy()
+            ref = W.dense_visible(idx_np, Sq, causal).sum(axis=(2, 3))
+            assert np.array_equal(got, ref), (name, Sq, Sk)
+            assert np.array_equal(W.count_visible(idx_np, 2, Sq, Sk, causal), ref), (name, Sq, Sk)
+
+
+def test_full_size_properties():
+    """At benchmark size: counts agree with the host formula and the class map
+    is consistent with the surviving-tile count (size-independent checks)."""
+    w = W.make_workload("causal_doc_8k_gqa")
+    idx = torch.from_numpy(w.idx).cuda()
+    got = fm.count_visible(idx, w.Sq, w.causal).cpu().numpy()
+    assert np.array_equal(got, W.count_visible(w.idx, w.B, w.Sq, w.Sk, w.causal))
+    info = fm.prepare_mask(idx, w.Sq, w.causal, 128, 64, want_count=True, want_class=True)
+    cls = info.tile_class.cpu().numpy()
+    assert np.array_equal((cls != 0).sum(-1), info.valid_block_count.cpu().numpy())
+    # every document diagonal tile is partial, far-away tiles are skipped
+    assert (cls[:, :, np.arange(64), np.arange(64) * 2] == 1).all()
+    assert (cls[:, :, 0, 2:] == 0).all()
