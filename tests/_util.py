@@ -41,7 +41,7 @@ def naive_lowp(q, k, v, do, idx, causal, sink, scale=None):
         bt = bt.repeat_interleave(Hq // bt.shape[1], dim=1)
         scores = scores + bt.to(scores.dtype)
         dead = torch.isinf(bt).all(dim=-1, keepdim=True)
-        scores = torch.where(dead, torch.full_like(scores, -1e9), scores)
+        scores = torch.where(dead, torch.full_like(scores, -3e4), scores)
     sk = None
     if sink is not None:
         sk = sink.detach().clone().to(q.device).requires_grad_(True)

@@ -62,7 +62,7 @@ def _run(kind, B, Sq, Sk, Hq, Hkv, d, dv, sink=False, seed=0, dtype=torch.bfloat
         per = [_mask(kind, B, Sq, Sk, seed + 1 + h)[0] for h in range(hm)]
         idx_np = np.ascontiguousarray(np.concatenate(per, axis=1))
     q, k, v, do, s = make_inputs(B, Sq, Sk, Hq, Hkv, d, dv, seed, dtype=dtype, sink=sink)
-    idx = None if idx_np is None else torch.from_numpy(idx_np).cuda()
+    idx = None if idx_np is None else torch.from_numpy(np.ascontiguousarray(idx_np).copy()).cuda()
     qc, kc, vc, doc = q.cuda(), k.cuda(), v.cuda(), do.cuda()
     got = run_product(qc, kc, vc, doc, idx, causal, s)
     ref = run_oracle(q, k, v, do, idx, causal, s)
@@ -146,7 +146,7 @@ def test_against_reference_golden(path):
 def test_deterministic_bitwise():
     idx_np, causal = _mask("causal_doc", 2, 512, 512, 21)
     q, k, v, do, s = make_inputs(2, 512, 512, 8, 2, 128, 128, 21, sink=True)
-    idx = torch.from_numpy(idx_np).cuda()
+    idx = torch.from_numpy(np.ascontiguousarray(idx_np).copy()).cuda()
     a = run_product(q.cuda(), k.cuda(), v.cuda(), do.cuda(), idx, causal, s, deterministic=True)
     for _ in range(3):
         b = run_product(q.cuda(), k.cuda(), v.cuda(), do.cuda(), idx, causal, s, deterministic=True)
@@ -159,7 +159,7 @@ def test_layout_invariance():
     (reference: tests/torch/test_flashmask.py:354-396)."""
     idx_np, causal = _mask("causal_doc", 1, 256, 256, 5)
     q, k, v, do, _ = make_inputs(1, 256, 256, 4, 2, 128, 128, 5)
-    idx = torch.from_numpy(idx_np).cuda()
+    idx = torch.from_numpy(np.ascontiguousarray(idx_np).copy()).cuda()
     a = run_product(q.cuda(), k.cuda(), v.cuda(), do.cuda(), idx, causal, None, deterministic=True)
 
     def bhsd(t):  # same values, [B,H,S,D] storage viewed as [B,S,H,D]

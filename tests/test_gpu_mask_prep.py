@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 
 def _masks(B, Sq, Sk, seed):
     rng = np.random.default_rng(seed)
-    docs = W.uniform_doc_lengths(rng, Sk, 7)
+    docs = W.uniform_doc_lengths(rng, Sk, min(7, Sk))
     yield "causal_doc", W.causal_document(B, Sq, Sk, docs)
     yield "bidir_doc", W.bidirectional_document(B, Sq, Sk, docs)
     yield "sliding_window", W.sliding_window(B, Sq, Sk, max(2, Sk // 9))
