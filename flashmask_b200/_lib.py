@@ -54,6 +54,7 @@ SIGNATURES = {
     "fm_fwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "fm_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(AttnArgs)]),
     "fm_bwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
+    "fm_kernel_status": (C.c_int, [C.POINTER(C.c_int), C.c_int]),
 }
 
 _lib = None

@@ -1,6 +1,7 @@
 // extern "C" entry points: argument validation, kernel-variant selection,
 // workspace carving.  No allocation, no host synchronisation.
 #include <cstdarg>
+#include <cstdlib>
 #include <cstring>
 
 #include "fm_attn_params.cuh"
@@ -34,7 +35,17 @@ bool bwd_sm100_supported(const fm_attn_args* a);
 int bwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s);
 size_t bwd_sm100_workspace_bytes(const fm_attn_args* a);
 
+int fwd_sm100_status(int* out, bool reset);
+
 static inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+// Kernel variant of the forward for (d, dv): the tcgen05 kernel covers
+// d = dv = 128; FLASHMASK_B200_FWD=mma forces the warp-MMA variant (A/B runs).
+static bool fwd_uses_sm100(int d, int dv) {
+  if (!(d == 128 && dv == 128)) return false;
+  const char* e = getenv("FLASHMASK_B200_FWD");
+  return !(e && strcmp(e, "mma") == 0);
+}
 
 static bool stride_ok(const int64_t* s) { return s[0] % 8 == 0 && s[1] % 8 == 0 && s[2] % 8 == 0; }
 
@@ -105,6 +116,7 @@ extern "C" const char* fm_last_error(void) { return g_err; }
 
 extern "C" int fm_fwd_tile_shape(int d, int dv, int* tile_m, int* tile_n) {
   FM_REQUIRE(tile_m && tile_n, FM_ERR_INVALID_ARGUMENT, "fm_fwd_tile_shape: NULL output");
+  if (fwd_uses_sm100(d, dv)) { *tile_m = 128; *tile_n = 128; return FM_OK; }
   int rc = fwd_mma_tile_shape(d, dv, tile_m, tile_n);
   if (rc != FM_OK) set_error("fm_fwd_tile_shape: unsupported head dims (d=%d, dv=%d)", d, dv);
   return rc;
@@ -128,6 +140,9 @@ extern "C" int fm_fwd(const fm_attn_args* a, void* stream) {
   AttnKParams p;
   fill_kparams(a, &p, false);
   p.md.nblk_pad = fm_mask_nblk_pad(a->Sk, tn);
+  if (fwd_uses_sm100(a->d, a->dv) && fwd_sm100_supported(a)) return fwd_sm100_launch(p, a, (cudaStream_t)stream);
+  FM_REQUIRE(!fwd_uses_sm100(a->d, a->dv), FM_ERR_INVALID_ARGUMENT,
+             "fm_fwd: q/k/v must be 16-byte aligned");
   return fwd_mma_launch(p, a->dtype, (cudaStream_t)stream);
 }
 
@@ -168,4 +183,9 @@ extern "C" int fm_bwd(const fm_attn_args* a, void* stream) {
   if (rc != FM_OK) return rc;
   if (a->sink) rc = bwd_dsink_launch(p, s);
   return rc;
+}
+
+extern "C" int fm_kernel_status(int* status, int reset) {
+  FM_REQUIRE(status != nullptr, FM_ERR_INVALID_ARGUMENT, "fm_kernel_status: NULL output");
+  return fwd_sm100_status(status, reset != 0);
 }

@@ -67,20 +67,23 @@ __device__ __forceinline__ Bounds4 load_bounds(const MaskDesc& md, const int32_t
   return b;
 }
 
-// Tile class of rows [ms, me) against K tile n from the per-tile reductions.
-// Predicates: skip iff every element is masked by the bounds, partial iff some
-// bound may cut through the tile; causal / ragged-edge geometry on top.
-__device__ __forceinline__ int classify_tile(const MaskDesc& md, int bh_mask, int n, int ms, int me,
-                                             int tile_n) {
+// Tile flags of rows [ms, me) against K tile n, from the per-tile reductions.
+// 0 = skipped (every element masked by the bounds or by causal geometry), else
+// bit 0 set plus the element masks the tile still needs:
+//   FM_TF_BOUNDS  some column bound may cut through the tile
+//   FM_TF_CAUSAL  the causal diagonal crosses the tile
+//   FM_TF_RAGGED  the tile hangs over the end of the key sequence
+constexpr uint32_t FM_TF_ACTIVE = 1, FM_TF_BOUNDS = 2, FM_TF_CAUSAL = 4, FM_TF_RAGGED = 8;
+
+__device__ __forceinline__ uint32_t tile_flags(const MaskDesc& md, int bh_mask, int n, int ms, int me,
+                                               int tile_n) {
   const int ns = n * tile_n;
   const int ne = min(ns + tile_n, md.Sk);
   const int off = md.Sk - md.Sq;
-  bool skip = false, needs = ne < ns + tile_n;
+  uint32_t flags = FM_TF_ACTIVE | (ne < ns + tile_n ? FM_TF_RAGGED : 0u);
   if (md.causal) {
-    const bool c_empty = ns > (me - 1 + off);
-    const bool c_full = (ne - 1) <= (ms + off);
-    skip = c_empty;
-    needs = needs || (!c_empty && !c_full);
+    if (ns > (me - 1 + off)) return 0;               // entirely in the future
+    if (!((ne - 1) <= (ms + off))) flags |= FM_TF_CAUSAL;
   }
   if (md.ncols) {
     const int32_t* mm = md.minmax + (size_t)bh_mask * md.nblk_pad + n;
@@ -105,10 +108,17 @@ __device__ __forceinline__ int classify_tile(const MaskDesc& md, int bh_mask, in
       fully = ms >= lts_max;
       part = me > lts_min;
     }
-    skip = skip || fully;
-    needs = needs || part;
+    if (fully) return 0;
+    if (part) flags |= FM_TF_BOUNDS;
   }
-  return skip ? FM_TILE_SKIP : (needs ? FM_TILE_PARTIAL : FM_TILE_FULL);
+  return flags;
+}
+
+// Three-way class of the same tile: skipped / partial (needs an element mask) / unmasked.
+__device__ __forceinline__ int classify_tile(const MaskDesc& md, int bh_mask, int n, int ms, int me,
+                                             int tile_n) {
+  const uint32_t f = tile_flags(md, bh_mask, n, ms, me, tile_n);
+  return f == 0 ? FM_TILE_SKIP : ((f & ~FM_TF_ACTIVE) ? FM_TILE_PARTIAL : FM_TILE_FULL);
 }
 
 // ---------------------------------------------------------------------------

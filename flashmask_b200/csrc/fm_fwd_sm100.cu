@@ -1,0 +1,503 @@
+// Forward attention on the 5th-generation tensor cores (tcgen05 / UMMA) for
+// d = dv = 128.
+//
+// One CTA owns 256 query rows of one (batch, q head) as two 128-row sub-tiles
+// that share every K/V tile.  Warp roles:
+//   warps 0-3   softmax of sub-tile 0 (thread t <-> row t, TMEM lane t)
+//   warps 4-7   softmax of sub-tile 1
+//   warp  8     TMA producer: Q once, then K and V tiles through a 4-slot ring,
+//               plus the column bounds of partial tiles (plain loads -> smem)
+//   warp  9     UMMA issuer (one elected thread): S_s = Q_s K^T into TMEM,
+//               O_s += P_s V with P_s read from TMEM; owns the TMEM allocation
+//   warp 10     builds the list of surviving K tiles with per-sub-tile flags
+//   warp 11     idle
+// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512);
+// P_s (bf16, 64 columns) overlays the upper half of S_s.
+// Online softmax keeps a stale running maximum and only rescales O when the
+// maximum grew by more than 2^8 (the rescale is done by the softmax warps
+// themselves).  Every mbarrier wait is bounded: on expiry the CTA raises an
+// abort flag, all roles unwind, TMEM is freed and a status word is set.
+#include "fm_attn_params.cuh"
+#include "fm_sm100.cuh"
+
+namespace fm {
+
+using namespace sm100;
+
+__device__ int g_fwd_status = 0;
+
+template <int D>
+struct FwdSm100Cfg {
+  static constexpr int BM = 128, BN = 128, NSTAGE = 4, NBND = 2, LIST_MAX = 2048;
+  static constexpr int NTHREADS = 384;
+  static constexpr int SUB = 128 * 128;                 // bytes of a 128-row x 64-col bf16 sub-tile
+  static constexpr int Q_BYTES = BM * D * 2;
+  static constexpr int SLOT_BYTES = BN * D * 2;
+  static constexpr int BND_BYTES = 128 * 4 * 4;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_KV = OFF_Q + 2 * Q_BYTES;
+  static constexpr int OFF_BND = OFF_KV + NSTAGE * SLOT_BYTES;
+  static constexpr int OFF_LIST = OFF_BND + NBND * BND_BYTES;
+  static constexpr int OFF_BAR = OFF_LIST + LIST_MAX * 4;
+  static constexpr int OFF_MISC = OFF_BAR + 32 * 8;
+  static constexpr int SMEM = OFF_MISC + 64 + 1024;     // + alignment slack
+  // barrier indices
+  static constexpr int B_QFULL = 0, B_KVFULL = 2, B_KVEMPTY = 2 + NSTAGE, B_SFULL = 2 + 2 * NSTAGE,
+                       B_PFULL = B_SFULL + 2, B_ODONE = B_PFULL + 2, B_BNDFULL = B_ODONE + 2,
+                       B_BNDEMPTY = B_BNDFULL + NBND, B_COUNT = B_BNDEMPTY + NBND;
+  static_assert(B_COUNT <= 32, "barrier storage");
+  static_assert(SMEM > 120 * 1024, "one CTA per SM is assumed by the 512-column TMEM allocation");
+};
+
+__device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
+
+template <int D, bool IS_BF16>
+__global__ void __launch_bounds__(384, 1)
+fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const AttnKParams p) {
+  using Cfg = FwdSm100Cfg<D>;
+  constexpr int DV = D;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t sQ = sbase + Cfg::OFF_Q, sKV = sbase + Cfg::OFF_KV;
+  uint32_t* list = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_LIST);
+  const uint32_t bars = sbase + Cfg::OFF_BAR;
+  volatile int* misc = reinterpret_cast<volatile int*>(smem + Cfg::OFF_MISC);
+  // misc[0] tmem base, [1] cnt, [2] cnt_s0, [3] cnt_s1, [4] abort
+  auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+
+  const int tid = threadIdx.x;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+  const int lane = tid & 31;
+  const int n_tiles = (p.Sq + 255) / 256;
+  const int t = n_tiles - 1 - blockIdx.x;
+  const int hq = blockIdx.y, b = blockIdx.z;
+  const int hk = hq / (p.Hq / p.Hkv);
+  const MaskDesc& md = p.md;
+  const int bh_mask = md.ncols ? ((md.mask_B == 1 ? 0 : b) * md.Hm + hq / (p.Hq / md.Hm)) : 0;
+  const int ms = t * 256;
+  const int off = p.Sk - p.Sq;
+
+  if (tid == 0) misc[4] = 0;
+  if (warp == 8 && lane == 0) {
+    mbar_init(bar(Cfg::B_QFULL + 0), 1); mbar_init(bar(Cfg::B_QFULL + 1), 1);
+    for (int i = 0; i < Cfg::NSTAGE; ++i) { mbar_init(bar(Cfg::B_KVFULL + i), 1); mbar_init(bar(Cfg::B_KVEMPTY + i), 1); }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(Cfg::B_SFULL + s), 1); mbar_init(bar(Cfg::B_PFULL + s), 128); mbar_init(bar(Cfg::B_ODONE + s), 1);
+    }
+    for (int i = 0; i < Cfg::NBND; ++i) { mbar_init(bar(Cfg::B_BNDFULL + i), 32); mbar_init(bar(Cfg::B_BNDEMPTY + i), 256); }
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 9) {
+    tmem_alloc(sbase + Cfg::OFF_MISC, 512);
+    tmem_relinquish();
+  }
+  if (warp == 10) {
+    // surviving K tiles, right to left, with the flags of both sub-tiles
+    const int nb = (p.Sk + 127) / 128;
+    const int me_tile = min(ms + 256, p.Sq);
+    int n_hi = nb;
+    if (md.causal) n_hi = max(0, min(nb, (me_tile + off + 127) / 128));
+    int cnt = 0, c0 = 0, c1 = 0;
+    for (int base = n_hi - 1; base >= 0; base -= 32) {
+      const int n = base - lane;
+      uint32_t f0 = 0, f1 = 0;
+      if (n >= 0) {
+        f0 = tile_flags(md, bh_mask, n, ms, min(ms + 128, p.Sq), 128);
+        if (ms + 128 < p.Sq) f1 = tile_flags(md, bh_mask, n, ms + 128, min(ms + 256, p.Sq), 128);
+      }
+      const bool keep = (f0 | f1) != 0;
+      const uint32_t bal = __ballot_sync(0xffffffffu, keep);
+      const int pos = cnt + __popc(bal & ((1u << lane) - 1u));
+      if (keep && pos < Cfg::LIST_MAX) list[pos] = (uint32_t)n | (f0 << 16) | (f1 << 20);
+      cnt += __popc(bal);
+      c0 += __popc(__ballot_sync(0xffffffffu, f0 != 0));
+      c1 += __popc(__ballot_sync(0xffffffffu, f1 != 0));
+    }
+    if (lane == 0) { misc[1] = min(cnt, Cfg::LIST_MAX); misc[2] = c0; misc[3] = c1; }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = (uint32_t)misc[0];
+  const int cnt = misc[1];
+  const int cnt_s[2] = {misc[2], misc[3]};
+  WaitCtx wc{misc + 4, global_timer_ns() + 2000000000ull};
+
+  if (warp < 8) {
+    // =========================== softmax warpgroups ===========================
+    setmaxnreg_inc<200>();
+    const int s = warp >> 2;
+    const int r = tid & 127;                   // row inside the sub-tile == TMEM lane
+    const int row = ms + 128 * s + r;
+    const uint32_t lane_field = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + lane_field + 128u * s;
+    const uint32_t tP = tS + 64u;
+    const uint32_t tO = tmem + lane_field + 256u + 128u * s;
+    const float scale_log2 = p.scale_log2;
+    float m_run = neg_inf(), l_run = 0.f;
+    int n_done = 0, nbnd = 0;
+    bool ok = true;
+    for (int i = 0; i < cnt && ok; ++i) {
+      const uint32_t e = list[i];
+      const uint32_t flags = (e >> (16 + 4 * s)) & 0xFu;
+      const bool any_bounds = (((e >> 16) | (e >> 20)) & FM_TF_BOUNDS) != 0;
+      const int bslot = nbnd % Cfg::NBND;
+      const uint32_t bpar = (uint32_t)(nbnd / Cfg::NBND) & 1u;
+      if (any_bounds) {
+        // every softmax thread passes through the full barrier of a bounds slot
+        // before releasing it, so a warpgroup that runs ahead (inactive on these
+        // tiles) cannot arrive twice within one phase of the empty barrier
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_BNDFULL + bslot), bpar, wc));
+        if (!ok) break;
+      }
+      if (flags) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_SFULL + s), (uint32_t)n_done & 1u, wc));
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t sr[128];
+        tmem_ld32(tS + 0, sr); tmem_ld32(tS + 32, sr + 32); tmem_ld32(tS + 64, sr + 64); tmem_ld32(tS + 96, sr + 96);
+        tc_wait_ld();
+        const uint32_t NEG = 0xff800000u;
+        if (flags & FM_TF_BOUNDS) {
+          const int4* bp = reinterpret_cast<const int4*>(smem + Cfg::OFF_BND + bslot * Cfg::BND_BYTES);
+          if (md.ncols == 1) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int4 v = bp[j];
+              if (row >= v.x) sr[4 * j] = NEG;
+              if (row >= v.y) sr[4 * j + 1] = NEG;
+              if (row >= v.z) sr[4 * j + 2] = NEG;
+              if (row >= v.w) sr[4 * j + 3] = NEG;
+            }
+          } else if (md.ncols == 2 && md.causal) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) {
+              const int4 v = bp[j];
+              if (row >= v.x && row < v.y) sr[2 * j] = NEG;
+              if (row >= v.z && row < v.w) sr[2 * j + 1] = NEG;
+            }
+          } else if (md.ncols == 2) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) {
+              const int4 v = bp[j];
+              if (row >= v.x || row < v.y) sr[2 * j] = NEG;
+              if (row >= v.z || row < v.w) sr[2 * j + 1] = NEG;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 128; ++j) {
+              const int4 v = bp[j];
+              if ((row >= v.x && row < v.y) || (row >= v.z && row < v.w)) sr[j] = NEG;
+            }
+          }
+        }
+        if (flags & (FM_TF_CAUSAL | FM_TF_RAGGED)) {
+          const int j0 = (int)(e & 0xFFFFu) * 128;
+          int jmax = p.Sk - 1 - j0;                      // last valid key column of this tile
+          if (md.causal) jmax = min(jmax, row + off - j0);
+#pragma unroll
+          for (int j = 0; j < 128; ++j)
+            if (j > jmax) sr[j] = NEG;
+        }
+        // ---- row maximum, lazy rescale ----
+        float mx0 = neg_inf(), mx1 = neg_inf(), mx2 = neg_inf(), mx3 = neg_inf();
+#pragma unroll
+        for (int j = 0; j < 128; j += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(sr[j])); mx1 = fmaxf(mx1, __uint_as_float(sr[j + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(sr[j + 2])); mx3 = fmaxf(mx3, __uint_as_float(sr[j + 3]));
+        }
+        const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2);
+        const bool need = (m_new - m_run) > 8.0f;
+        float alpha = 1.f;
+        if (need) {
+          alpha = fast_exp2(m_run - m_new);             // m_run == -inf -> 0
+          m_run = m_new;
+          l_run *= alpha;
+        }
+        if (__any_sync(0xffffffffu, need) && n_done > 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_ODONE + s), (uint32_t)(n_done - 1) & 1u, wc));
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < DV / 32; ++c) {
+            uint32_t orr[32];
+            tmem_ld32(tO + 32 * c, orr);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * alpha);
+            tmem_st32(tO + 32 * c, orr);
+          }
+        }
+        // ---- P = exp2(S * scale_log2 - m), bf16 into TMEM ----
+        const float m_use = (m_run == neg_inf()) ? 0.f : m_run;
+        float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[32 * c + 2 * j]), scale_log2, -m_use));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[32 * c + 2 * j + 1]), scale_log2, -m_use));
+            ls0 += p0; ls1 += p1;
+            pk[j] = pack2<IS_BF16>(p0, p1);
+          }
+          tmem_st16(tP + 16 * c, pk);
+        }
+        l_run += ls0 + ls1;
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar(Cfg::B_PFULL + s));
+        ++n_done;
+      }
+      if (any_bounds) {
+        mbar_arrive(bar(Cfg::B_BNDEMPTY + bslot));
+        ++nbnd;
+      }
+    }
+    // ---- epilogue: O / l -> bf16 -> smem staging -> coalesced stores; LSE ----
+    if (ok && n_done > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_ODONE + s), (uint32_t)(n_done - 1) & 1u, wc));
+      tc_fence_after();
+    }
+    if (ok) {
+      const float m_fin = (m_run == neg_inf()) ? 0.f : m_run;
+      float l_tot = l_run;
+      if (p.sink) l_tot += fast_exp2(p.sink[hq] * kLog2e - m_fin);
+      const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+      uint8_t* stage = smem + Cfg::OFF_Q + s * Cfg::Q_BYTES;   // Q_s is no longer needed
+#pragma unroll
+      for (int c = 0; c < DV / 32; ++c) {
+        uint32_t orr[32];
+        if (n_done > 0) {
+          tmem_ld32(tO + 32 * c, orr);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) orr[j] = 0u;
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 v;
+          v.x = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 0]) * inv, __uint_as_float(orr[8 * q4 + 1]) * inv);
+          v.y = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 2]) * inv, __uint_as_float(orr[8 * q4 + 3]) * inv);
+          v.z = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 4]) * inv, __uint_as_float(orr[8 * q4 + 5]) * inv);
+          v.w = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 6]) * inv, __uint_as_float(orr[8 * q4 + 7]) * inv);
+          const int chunk = 4 * c + q4;                 // 16-byte chunk inside the row
+          *reinterpret_cast<uint4*>(stage + r * (DV * 2) + ((chunk ^ (r & (DV / 8 - 1))) << 4)) = v;
+        }
+      }
+      if (row < p.Sq)
+        p.lse[((int64_t)b * p.Hq + hq) * p.Sq + row] = l_tot > 0.f ? (m_fin + log2f(l_tot)) * kLn2 : neg_inf();
+      named_bar_sync(1 + s, 128);
+      uint16_t* go = reinterpret_cast<uint16_t*>(p.o) + b * p.o_b + (int64_t)(ms + 128 * s) * p.o_s + hq * p.o_h;
+      constexpr int CH = DV / 8;
+#pragma unroll 4
+      for (int idx = r; idx < 128 * CH; idx += 128) {
+        const int rr = idx / CH, cc = idx % CH;
+        if (ms + 128 * s + rr < p.Sq) {
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * (DV * 2) + ((cc ^ (rr & (CH - 1))) << 4));
+          *reinterpret_cast<uint4*>(go + (int64_t)rr * p.o_s + cc * 8) = v;
+        }
+      }
+    }
+  } else {
+    setmaxnreg_dec<64>();
+    if (warp == 8) {
+      // =========================== TMA / bounds producer ===========================
+      if (lane == 0) {
+        for (int s = 0; s < 2; ++s) {
+          if (cnt_s[s] > 0) {
+            mbar_arrive_expect_tx(bar(Cfg::B_QFULL + s), Cfg::Q_BYTES);
+            for (int dc = 0; dc < D / 64; ++dc)
+              tma_load_4d(sQ + s * Cfg::Q_BYTES + dc * Cfg::SUB, &tm_q, bar(Cfg::B_QFULL + s), dc * 64, hq,
+                          ms + 128 * s, b);
+          }
+        }
+      }
+      int nbnd = 0;
+      bool ok = true;
+      for (int i = 0; i < cnt && ok; ++i) {
+        const uint32_t e = list[i];
+        const int j0 = (int)(e & 0xFFFFu) * 128;
+        if (lane == 0) {
+          for (int kv = 0; kv < 2 && ok; ++kv) {
+            const int k = 2 * i + kv, slot = k % Cfg::NSTAGE;
+            const uint32_t par = ((uint32_t)(k / Cfg::NSTAGE) & 1u) ^ 1u;
+            ok = mbar_wait(bar(Cfg::B_KVEMPTY + slot), par, wc);
+            if (!ok) break;
+            mbar_arrive_expect_tx(bar(Cfg::B_KVFULL + slot), Cfg::SLOT_BYTES);
+            for (int dc = 0; dc < D / 64; ++dc)
+              tma_load_4d(sKV + slot * Cfg::SLOT_BYTES + dc * Cfg::SUB, kv == 0 ? &tm_k : &tm_v,
+                          bar(Cfg::B_KVFULL + slot), dc * 64, hk, j0, b);
+          }
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if ((((e >> 16) | (e >> 20)) & FM_TF_BOUNDS) != 0) {
+          const int bslot = nbnd % Cfg::NBND;
+          const uint32_t par = ((uint32_t)(nbnd / Cfg::NBND) & 1u) ^ 1u;
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_BNDEMPTY + bslot), par, wc));
+          if (!ok) break;
+          int* dst = reinterpret_cast<int*>(smem + Cfg::OFF_BND + bslot * Cfg::BND_BYTES);
+          const int32_t* src = md.mask + ((size_t)bh_mask * p.Sk + j0) * md.ncols;
+          const int valid = min(128, p.Sk - j0) * md.ncols;
+          for (int x = lane; x < 128 * md.ncols; x += 32) dst[x] = x < valid ? __ldg(src + x) : 0;
+          mbar_arrive(bar(Cfg::B_BNDFULL + bslot));
+          ++nbnd;
+        }
+      }
+    } else if (warp == 9) {
+      // =========================== UMMA issuer ===========================
+      if (lane == 0) {
+        constexpr uint32_t idesc_qk = make_idesc(IS_BF16, 128, 128, 0, 0);
+        constexpr uint32_t idesc_pv = make_idesc(IS_BF16, 128, DV, 0, 1);
+        int npv[2] = {0, 0};
+        bool q_ready[2] = {false, false};
+        bool ok = true;
+        auto issue_qk = [&](int s, int i) {
+          const int k = 2 * i, slot = k % Cfg::NSTAGE;
+          ok = ok && mbar_wait(bar(Cfg::B_KVFULL + slot), (uint32_t)(k / Cfg::NSTAGE) & 1u, wc);
+          if (ok && !q_ready[s]) { ok = mbar_wait(bar(Cfg::B_QFULL + s), 0u, wc); q_ready[s] = true; }
+          if (!ok) return;
+          tc_fence_after();
+          const uint32_t a0 = sQ + s * Cfg::Q_BYTES, b0 = sKV + slot * Cfg::SLOT_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t o = (uint32_t)(kk >> 2) * Cfg::SUB + (uint32_t)(kk & 3) * 32u;
+            umma_ss(tmem + 128u * s, make_sdesc(a0 + o, 16, 1024), make_sdesc(b0 + o, 16, 1024), idesc_qk,
+                    kk > 0 ? 1u : 0u);
+          }
+          tc_commit(bar(Cfg::B_SFULL + s));
+        };
+        auto issue_pv = [&](int s, int i) {
+          const int k = 2 * i + 1, slot = k % Cfg::NSTAGE;
+          ok = ok && mbar_wait(bar(Cfg::B_KVFULL + slot), (uint32_t)(k / Cfg::NSTAGE) & 1u, wc);
+          ok = ok && mbar_wait(bar(Cfg::B_PFULL + s), (uint32_t)npv[s] & 1u, wc);
+          if (!ok) return;
+          tc_fence_after();
+          const uint32_t v0 = sKV + slot * Cfg::SLOT_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ts(tmem + 256u + 128u * s, tmem + 128u * s + 64u + 8u * kk,
+                    make_sdesc(v0 + kk * 2048u, Cfg::SUB, 1024), idesc_pv, (npv[s] > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(bar(Cfg::B_ODONE + s));
+          ++npv[s];
+        };
+        if (cnt > 0) {
+          const uint32_t e = list[0];
+          for (int s = 0; s < 2; ++s)
+            if ((e >> (16 + 4 * s)) & 0xFu) issue_qk(s, 0);
+          if (ok) tc_commit(bar(Cfg::B_KVEMPTY + 0));
+        }
+        for (int i = 0; i < cnt && ok; ++i) {
+          const uint32_t e = list[i];
+          const uint32_t en = (i + 1 < cnt) ? list[i + 1] : 0u;
+          for (int s = 0; s < 2 && ok; ++s) {
+            if ((e >> (16 + 4 * s)) & 0xFu) issue_pv(s, i);
+            if (ok && ((en >> (16 + 4 * s)) & 0xFu)) issue_qk(s, i + 1);
+          }
+          if (!ok) break;
+          tc_commit(bar(Cfg::B_KVEMPTY + (2 * i + 1) % Cfg::NSTAGE));
+          if (i + 1 < cnt) tc_commit(bar(Cfg::B_KVEMPTY + (2 * i + 2) % Cfg::NSTAGE));
+        }
+      }
+      __syncwarp();
+    }
+  }
+
+  // =========================== teardown ===========================
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const bool aborted = misc[4] != 0;
+  if (aborted) {
+    // give copies and MMAs still in flight a bounded time to land before the
+    // shared and tensor memory of this CTA are released
+    const uint64_t t_end = global_timer_ns() + 200000ull;
+    while (global_timer_ns() < t_end) __nanosleep(1000);
+    if (tid == 0) atomicExch(&g_fwd_status, FM_ERR_TIMEOUT);
+  }
+  if (warp == 9) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------
+// host
+// ---------------------------------------------------------------------------
+namespace sm100 {
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+int make_bshd_tmap(CUtensorMap* out, const void* base, int dtype, int B, int S, int H, int D, int64_t sb,
+                   int64_t ss, int64_t sh, int box_rows) {
+  EncodeTiledFn enc = get_encode_tiled();
+  FM_REQUIRE(enc != nullptr, FM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)B};
+  const cuuint64_t strides[3] = {(cuuint64_t)sh * 2, (cuuint64_t)ss * 2, (cuuint64_t)(sb > 0 ? sb : ss * S) * 2};
+  const cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = enc(out, dtype == FM_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                         4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  FM_REQUIRE(r == CUDA_SUCCESS, FM_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return FM_OK;
+}
+
+}  // namespace sm100
+
+bool fwd_sm100_supported(const fm_attn_args* a) {
+  if (!(a->d == 128 && a->dv == 128)) return false;
+  if (((uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v) & 15) return false;
+  return true;
+}
+
+template <int D, bool IS_BF16>
+static int launch_fwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
+  using Cfg = FwdSm100Cfg<D>;
+  FM_REQUIRE((a->Sk + 127) / 128 <= Cfg::LIST_MAX, FM_ERR_UNSUPPORTED,
+             "forward: Sk=%d exceeds the %d keys this kernel variant indexes", a->Sk, Cfg::LIST_MAX * 128);
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_bshd_tmap(&tq, a->q, a->dtype, a->B, a->Sq, a->Hq, a->d, a->q_stride[0], a->q_stride[1], a->q_stride[2], 128))) return rc;
+  if ((rc = make_bshd_tmap(&tk, a->k, a->dtype, a->B, a->Sk, a->Hkv, a->d, a->k_stride[0], a->k_stride[1], a->k_stride[2], 128))) return rc;
+  if ((rc = make_bshd_tmap(&tv, a->v, a->dtype, a->B, a->Sk, a->Hkv, a->dv, a->v_stride[0], a->v_stride[1], a->v_stride[2], 128))) return rc;
+  auto kern = fwd_sm100_kernel<D, IS_BF16>;
+  FM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+  dim3 grid((p.Sq + 255) / 256, p.Hq, p.B);
+  kern<<<grid, Cfg::NTHREADS, Cfg::SMEM, s>>>(tq, tk, tv, p);
+  FM_CUDA_TRY(cudaGetLastError());
+  return FM_OK;
+}
+
+int fwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
+  const bool bf = a->dtype == FM_DTYPE_BF16;
+  return bf ? launch_fwd_sm100<128, true>(p, a, s) : launch_fwd_sm100<128, false>(p, a, s);
+}
+
+int fwd_sm100_status(int* out, bool reset) {
+  int v = 0;
+  FM_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_fwd_status, sizeof(int)));
+  if (reset && v != 0) {
+    const int z = 0;
+    FM_CUDA_TRY(cudaMemcpyToSymbol(g_fwd_status, &z, sizeof(int)));
+  }
+  *out = v;
+  return FM_OK;
+}
+
+}  // namespace fm

@@ -151,6 +151,14 @@ FM_API int fm_bwd_tile_shape(int d, int dv, int* tile_m, int* tile_n);
  * Uses no workspace. */
 FM_API int fm_fwd(const fm_attn_args* args, void* stream);
 
+/* Device-side status of the kernels that wait on barriers (the tcgen05
+ * variants): every wait is bounded, and a wait that ran out makes its CTA
+ * unwind and record FM_ERR_TIMEOUT here instead of hanging.  Synchronises the
+ * device (debug / test use; not called on the hot path).  `reset` != 0 clears
+ * the word.  The reference instead traps the GPU from its spin watchdog
+ * (flashmask/cute/barrier.py:95-148). */
+FM_API int fm_kernel_status(int* status, int reset);
+
 /* Backward: dQ, dK, dV (and dsink when sink != NULL).
  * Replaces _flash_attn_bwd (flashmask/cute/ops/bwd.py:56-1261): preprocess
  * (flash_bwd_preprocess.py:184-342), main (flash_bwd_sm100.py:1435-),

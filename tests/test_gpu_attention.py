@@ -14,6 +14,27 @@ from _util import (assert_lse, assert_parity, make_inputs, naive_lowp, run_oracl
 
 pytestmark = pytest.mark.gpu
 
+
+@pytest.fixture(params=["sm100", "mma"])
+def fwd_variant(request):
+    """d = dv = 128 has two forward kernels: the tcgen05 one (default) and the
+    warp-MMA one; FLASHMASK_B200_FWD selects per call."""
+    old = os.environ.get("FLASHMASK_B200_FWD")
+    os.environ["FLASHMASK_B200_FWD"] = request.param
+    yield request.param
+    if old is None:
+        os.environ.pop("FLASHMASK_B200_FWD", None)
+    else:
+        os.environ["FLASHMASK_B200_FWD"] = old
+
+
+def _kernel_status():
+    import ctypes as C
+    from flashmask_b200 import _lib
+    v = C.c_int(0)
+    _lib.check(_lib.load().fm_kernel_status(C.byref(v), 1), "fm_kernel_status")
+    return v.value
+
 GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "attention_*.npz")))
 
 
@@ -77,16 +98,21 @@ def _run(kind, B, Sq, Sk, Hq, Hkv, d, dv, sink=False, seed=0, dtype=torch.bfloat
 
 
 @pytest.mark.parametrize("kind", MASKS)
-def test_masks_d128_gqa(kind):
+def test_masks_d128_gqa(kind, fwd_variant):
     _run(kind, 2, 384, 384, 4, 2, 128, 128, seed=11)
+    _run(kind, 1, 1024, 1024, 2, 1, 128, 128, seed=12)
+    assert _kernel_status() == 0
 
 
 @pytest.mark.parametrize("kind", ["causal_doc", "bidir_doc", "four_column", "none_causal"])
-def test_ragged_shapes(kind):
+def test_ragged_shapes(kind, fwd_variant):
     # sequence lengths that are not multiples of any tile, Sq != Sk
     _run(kind, 1, 300, 300, 2, 2, 128, 128, seed=3)
     if kind in ("causal_doc", "none_causal"):
         _run(kind, 1, 203, 333, 2, 1, 64, 64, seed=4)
+        _run(kind, 1, 203, 333, 2, 1, 128, 128, seed=4)
+        _run(kind, 2, 333, 203, 2, 2, 128, 128, seed=4)
+    assert _kernel_status() == 0
 
 
 @pytest.mark.parametrize("d,dv,Hq,Hkv", [(64, 64, 2, 2), (80, 80, 2, 1), (128, 128, 4, 1),
@@ -98,16 +124,23 @@ def test_head_dims(kind, d, dv, Hq, Hkv):
 
 
 @pytest.mark.parametrize("kind", ["none_causal", "causal_doc", "random_eviction"])
-def test_sink(kind):
+def test_sink(kind, fwd_variant):
     _run(kind, 2, 256, 256, 4, 2, 128, 128, sink=True, seed=7)
 
 
-def test_mask_heads_per_kv_head():
+def test_mask_heads_per_kv_head(fwd_variant):
     _run("causal_doc", 2, 256, 256, 4, 2, 128, 128, seed=8, hm=2)
 
 
-def test_fp16():
+def test_fp16(fwd_variant):
     _run("causal_doc", 1, 256, 256, 2, 2, 128, 128, seed=9, dtype=torch.float16)
+
+
+def test_long_rows_many_tiles(fwd_variant):
+    """Enough K tiles per Q tile to wrap the K/V ring and the bounds slots many times."""
+    _run("random_eviction", 1, 2048, 2048, 2, 1, 128, 128, seed=13)
+    _run("sliding_window", 1, 2048, 2048, 1, 1, 128, 128, seed=14)
+    assert _kernel_status() == 0
 
 
 def test_cpu_config_shape():
