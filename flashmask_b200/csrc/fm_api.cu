@@ -189,3 +189,72 @@ extern "C" int fm_kernel_status(int* status, int reset) {
   FM_REQUIRE(status != nullptr, FM_ERR_INVALID_ARGUMENT, "fm_kernel_status: NULL output");
   return fwd_sm100_status(status, reset != 0);
 }
+
+// ---------------------------------------------------------------------------
+// Backward for callers that must not allocate
+// ---------------------------------------------------------------------------
+// Row-statistics scratch of the backward (rowsum(O*dO) and LSE*log2(e), one
+// float each per (batch, q head, padded query row)) held in the library image
+// instead of a caller workspace.  Every GPU that loads the library carries
+// these 8 MiB until the process exits.
+#define FM_STATIC_SCRATCH_ROWS (1 << 20)
+static __device__ __align__(256) float g_bwd_row_scratch[2 * FM_STATIC_SCRATCH_ROWS];
+
+// Device address of the array above, per device ordinal.  In host code the
+// array's name is only a handle; the address a kernel can use comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+static float* g_bwd_row_scratch_addr[64] = {nullptr};
+
+static int static_scratch_for_current_device(float** out) {
+  int dev = -1;
+  FM_CUDA_TRY(cudaGetDevice(&dev));
+  FM_REQUIRE(dev >= 0 && dev < 64, FM_ERR_UNSUPPORTED, "fm_bwd_static_scratch: device ordinal %d not supported", dev);
+  if (g_bwd_row_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    FM_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_bwd_row_scratch));
+    FM_REQUIRE(ptr != nullptr, FM_ERR_CUDA, "fm_bwd_static_scratch: cudaGetSymbolAddress returned NULL");
+    g_bwd_row_scratch_addr[dev] = static_cast<float*>(ptr);
+  }
+  *out = g_bwd_row_scratch_addr[dev];
+  return FM_OK;
+}
+
+extern "C" int fm_bwd_static_scratch(const fm_attn_args* a, void* stream) {
+  int rc = validate_common(a, "fm_bwd_static_scratch");
+  if (rc != FM_OK) return rc;
+  FM_REQUIRE(a->d_o && a->dq && a->dk && a->dv_out, FM_ERR_INVALID_ARGUMENT,
+             "fm_bwd_static_scratch: d_o/dq/dk/dv must not be NULL");
+  FM_REQUIRE(stride_ok(a->do_stride) && stride_ok(a->dq_stride) && stride_ok(a->dk_stride) &&
+                 stride_ok(a->dv_stride),
+             FM_ERR_INVALID_ARGUMENT, "fm_bwd_static_scratch: strides must be multiples of 8 elements");
+  FM_REQUIRE(!(a->sink && !a->dsink), FM_ERR_INVALID_ARGUMENT,
+             "fm_bwd_static_scratch: sink given but dsink is NULL");
+  int tm, tn;
+  rc = bwd_mma_tile_shape(a->d, a->dv, &tm, &tn);
+  FM_REQUIRE(rc == FM_OK, FM_ERR_UNSUPPORTED, "fm_bwd_static_scratch: unsupported head dims (d=%d, dv=%d)",
+             a->d, a->dv);
+  FM_REQUIRE(a->ncols == 0 || a->tile_n == tn, FM_ERR_INVALID_ARGUMENT,
+             "fm_bwd_static_scratch: minmax was prepared for tile_n=%d, this variant needs %d", a->tile_n, tn);
+  const size_t rows = (size_t)a->B * a->Hq * round_up(a->Sq, 128);
+  FM_REQUIRE(rows <= (size_t)FM_STATIC_SCRATCH_ROWS, FM_ERR_WORKSPACE,
+             "fm_bwd_static_scratch: B*Hq*roundup(Sq,128) = %zu rows exceeds the built-in scratch of %d rows; "
+             "use fm_bwd with a caller workspace",
+             rows, FM_STATIC_SCRATCH_ROWS);
+  float* scratch = nullptr;
+  rc = static_scratch_for_current_device(&scratch);
+  if (rc != FM_OK) return rc;
+  AttnKParams p;
+  fill_kparams(a, &p, true);
+  p.md.nblk_pad = fm_mask_nblk_pad(a->Sk, tn);
+  // Both halves are fully rewritten by the preprocess kernel for every row the
+  // later kernels read, so nothing left by an earlier call has to be cleared.
+  p.dpsum = scratch;
+  p.lse_log2 = scratch + rows;
+  cudaStream_t s = (cudaStream_t)stream;
+  rc = bwd_preprocess_launch(p, a->dtype, s);
+  if (rc != FM_OK) return rc;
+  rc = bwd_mma_launch(p, a->dtype, s);
+  if (rc != FM_OK) return rc;
+  if (a->sink) rc = bwd_dsink_launch(p, s);
+  return rc;
+}

@@ -168,6 +168,30 @@ FM_API int fm_kernel_status(int* status, int reset);
 FM_API size_t fm_bwd_workspace_bytes(const fm_attn_args* args);
 FM_API int fm_bwd(const fm_attn_args* args, void* stream);
 
+/*
+ * Backward without any allocation, for callers that cannot provide device
+ * memory of their own at call time: code running under a memory pool that is
+ * frozen (an inference / training runtime that sized its arena at start-up),
+ * a host thread that is not allowed to touch the CUDA allocator, or a plug-in
+ * boundary where the caller only owns the tensors it passes.  It has no
+ * counterpart in the reference, whose backward always allocates its own
+ * workspaces (flashmask/cute/ops/bwd.py:358-499).
+ *
+ * Same arguments and results as fm_bwd, except that args->workspace is
+ * ignored: the per-row scratch lives in a fixed 8 MiB array inside the library
+ * image on every GPU that loads it.  Limit: B * Hq * roundup(Sq, 128) must not
+ * exceed 1,048,576 rows (e.g. B=2, Hq=32, Sq=8192 uses half of it); larger
+ * problems are rejected with FM_ERR_WORKSPACE before anything is launched.
+ * The call makes no cudaMalloc / cudaFree and uses no allocating library
+ * routine.  The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress with that device current), so make that first call
+ * outside of any stream capture.  All calls on a device share the one array:
+ * two calls whose kernels may overlap on the GPU (different streams without an
+ * ordering between them) race on it; calls on one stream are safe, and a call
+ * never depends on what an earlier call left in the array.
+ */
+FM_API int fm_bwd_static_scratch(const fm_attn_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
