@@ -36,6 +36,7 @@ int bwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s
 size_t bwd_sm100_workspace_bytes(const fm_attn_args* a);
 
 int fwd_sm100_status(int* out, bool reset);
+int bwd_sm100_status(int* out, bool reset);
 
 static inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
@@ -68,8 +69,8 @@ static int validate_common(const fm_attn_args* a, const char* who) {
              "%s: ncols must be 0, 1, 2 or 4", who);
   if (a->ncols) {
     FM_REQUIRE(a->mask && a->minmax, FM_ERR_INVALID_ARGUMENT, "%s: mask given but mask/minmax is NULL", who);
-    FM_REQUIRE(a->Hm == 1 || a->Hm == a->Hkv || a->Hm == a->Hq, FM_ERR_INVALID_ARGUMENT,
-               "%s: mask heads (%d) must be 1, Hkv or Hq", who, a->Hm);
+    FM_REQUIRE(a->Hm == 1 || a->Hm == a->Hkv, FM_ERR_INVALID_ARGUMENT,
+               "%s: mask heads (%d) must be 1 or Hkv", who, a->Hm);
     FM_REQUIRE(a->mask_B == a->B || a->mask_B == 1, FM_ERR_INVALID_ARGUMENT,
                "%s: mask batch (%d) must be B or 1", who, a->mask_B);
     FM_REQUIRE(!(a->ncols == 1 && !a->causal) && !(a->ncols == 4 && a->causal), FM_ERR_INVALID_ARGUMENT,
@@ -114,6 +115,27 @@ using namespace fm;
 extern "C" const char* fm_version(void) { return "flashmask_b200 0.1.0 sm_100a"; }
 extern "C" const char* fm_last_error(void) { return g_err; }
 
+static bool bwd_uses_sm100(int d, int dv) {
+  if (!(d == 128 && dv == 128)) return false;
+  const char* e = getenv("FLASHMASK_B200_BWD");
+  return !(e && strcmp(e, "mma") == 0);
+}
+
+// preprocess -> main kernels of the selected variant -> dsink, on one stream
+static int run_bwd_kernels(const fm_attn_args* a, const AttnKParams& p, cudaStream_t s) {
+  int rc = bwd_preprocess_launch(p, a->dtype, s);
+  if (rc != FM_OK) return rc;
+  if (bwd_uses_sm100(a->d, a->dv)) {
+    FM_REQUIRE(bwd_sm100_supported(a), FM_ERR_INVALID_ARGUMENT, "backward: q/k/v/d_o must be 16-byte aligned");
+    rc = bwd_sm100_launch(p, a, s);
+  } else {
+    rc = bwd_mma_launch(p, a->dtype, s);
+  }
+  if (rc != FM_OK) return rc;
+  if (a->sink) rc = bwd_dsink_launch(p, s);
+  return rc;
+}
+
 extern "C" int fm_fwd_tile_shape(int d, int dv, int* tile_m, int* tile_n) {
   FM_REQUIRE(tile_m && tile_n, FM_ERR_INVALID_ARGUMENT, "fm_fwd_tile_shape: NULL output");
   if (fwd_uses_sm100(d, dv)) { *tile_m = 128; *tile_n = 128; return FM_OK; }
@@ -124,6 +146,7 @@ extern "C" int fm_fwd_tile_shape(int d, int dv, int* tile_m, int* tile_n) {
 
 extern "C" int fm_bwd_tile_shape(int d, int dv, int* tile_m, int* tile_n) {
   FM_REQUIRE(tile_m && tile_n, FM_ERR_INVALID_ARGUMENT, "fm_bwd_tile_shape: NULL output");
+  if (bwd_uses_sm100(d, dv)) { *tile_m = 64; *tile_n = 128; return FM_OK; }
   int rc = bwd_mma_tile_shape(d, dv, tile_m, tile_n);
   if (rc != FM_OK) set_error("fm_bwd_tile_shape: unsupported head dims (d=%d, dv=%d)", d, dv);
   return rc;
@@ -177,17 +200,17 @@ extern "C" int fm_bwd(const fm_attn_args* a, void* stream) {
   p.dpsum = reinterpret_cast<float*>(a->workspace);
   p.lse_log2 = p.dpsum + rows;
   cudaStream_t s = (cudaStream_t)stream;
-  rc = bwd_preprocess_launch(p, a->dtype, s);
-  if (rc != FM_OK) return rc;
-  rc = bwd_mma_launch(p, a->dtype, s);
-  if (rc != FM_OK) return rc;
-  if (a->sink) rc = bwd_dsink_launch(p, s);
-  return rc;
+  return run_bwd_kernels(a, p, s);
 }
 
 extern "C" int fm_kernel_status(int* status, int reset) {
   FM_REQUIRE(status != nullptr, FM_ERR_INVALID_ARGUMENT, "fm_kernel_status: NULL output");
-  return fwd_sm100_status(status, reset != 0);
+  int f = 0, bw = 0;
+  int rc = fwd_sm100_status(&f, reset != 0);
+  if (rc != FM_OK) return rc;
+  rc = bwd_sm100_status(&bw, reset != 0);
+  *status = f ? f : bw;
+  return rc;
 }
 
 // ---------------------------------------------------------------------------
@@ -230,9 +253,8 @@ extern "C" int fm_bwd_static_scratch(const fm_attn_args* a, void* stream) {
   FM_REQUIRE(!(a->sink && !a->dsink), FM_ERR_INVALID_ARGUMENT,
              "fm_bwd_static_scratch: sink given but dsink is NULL");
   int tm, tn;
-  rc = bwd_mma_tile_shape(a->d, a->dv, &tm, &tn);
-  FM_REQUIRE(rc == FM_OK, FM_ERR_UNSUPPORTED, "fm_bwd_static_scratch: unsupported head dims (d=%d, dv=%d)",
-             a->d, a->dv);
+  rc = fm_bwd_tile_shape(a->d, a->dv, &tm, &tn);
+  if (rc != FM_OK) return rc;
   FM_REQUIRE(a->ncols == 0 || a->tile_n == tn, FM_ERR_INVALID_ARGUMENT,
              "fm_bwd_static_scratch: minmax was prepared for tile_n=%d, this variant needs %d", a->tile_n, tn);
   const size_t rows = (size_t)a->B * a->Hq * round_up(a->Sq, 128);
@@ -250,11 +272,5 @@ extern "C" int fm_bwd_static_scratch(const fm_attn_args* a, void* stream) {
   // later kernels read, so nothing left by an earlier call has to be cleared.
   p.dpsum = scratch;
   p.lse_log2 = scratch + rows;
-  cudaStream_t s = (cudaStream_t)stream;
-  rc = bwd_preprocess_launch(p, a->dtype, s);
-  if (rc != FM_OK) return rc;
-  rc = bwd_mma_launch(p, a->dtype, s);
-  if (rc != FM_OK) return rc;
-  if (a->sink) rc = bwd_dsink_launch(p, s);
-  return rc;
+  return run_bwd_kernels(a, p, (cudaStream_t)stream);
 }

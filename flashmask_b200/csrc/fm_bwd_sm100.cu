@@ -1,0 +1,548 @@
+// Backward attention on the 5th-generation tensor cores (tcgen05 / UMMA) for
+// d = dv = 128, as two kernels that share one pipeline skeleton:
+//
+//   MODE_DKDV  one CTA per (128-key tile, kv head, batch).  K and V stay in
+//              shared memory; 64-row halves of Q and dO stream through a ring
+//              for every q head of the GQA group.  TMEM lanes are keys:
+//                S^T = K Q^T, dP^T = V dO^T            (M=128 keys, N=64 queries)
+//                dV += P^T dO, dK += dS^T Q             (A from TMEM, M=128, N=128, K=64)
+//   MODE_DQ    one CTA per (128-query tile, q head, batch).  Q and dO stay in
+//              shared memory; 64-row halves of K and V stream.  TMEM lanes are
+//              queries:  S = Q K^T, dP = dO V^T, dQ += dS K.
+//
+// Work items are the 64-row half tiles that the mask classification keeps; item
+// k is computed by softmax warpgroup k%2 out of score buffers k%2, so the
+// tensor pipe works on one item while the other warpgroup does exp2 / dS.
+// Every output element has exactly one owner CTA and a fixed summation order:
+// the gradients are bitwise reproducible and need neither atomics nor fp32
+// accumulators in global memory.
+//
+// Warp roles: 0-3 / 4-7 compute warpgroups, 8 TMA producer, 9 UMMA issuer
+// (owns TMEM), 10 item-list builder, 11 idle.  All waits are bounded.
+#include "fm_attn_params.cuh"
+#include "fm_sm100.cuh"
+
+namespace fm {
+
+using namespace sm100;
+
+__device__ int g_bwd_status = 0;
+
+constexpr int MODE_DKDV = 0, MODE_DQ = 1;
+
+struct BwdSm100Cfg {
+  static constexpr int NSLOT = 4, LIST_MAX = 2048, NTHREADS = 384;
+  static constexpr int TILE_BYTES = 128 * 128 * 2;     // 128 rows x 128 cols bf16
+  static constexpr int SUB128 = 128 * 128;             // 128-row x 64-col sub-tile (bytes)
+  static constexpr int SUB64 = 64 * 128;               // 64-row x 64-col sub-tile (bytes)
+  static constexpr int HALF_BYTES = 2 * SUB64;         // one operand of a half tile
+  static constexpr int SLOT_BYTES = 2 * HALF_BYTES;    // both operands
+  static constexpr int AUX_BYTES = 1024;
+  static constexpr int OFF_STAT = 0;
+  static constexpr int OFF_RING = OFF_STAT + 2 * TILE_BYTES;
+  static constexpr int OFF_AUX = OFF_RING + NSLOT * SLOT_BYTES;
+  static constexpr int OFF_LIST = OFF_AUX + NSLOT * AUX_BYTES;
+  static constexpr int OFF_BAR = OFF_LIST + LIST_MAX * 4;
+  static constexpr int OFF_MISC = OFF_BAR + 32 * 8;
+  static constexpr int SMEM = OFF_MISC + 64 + 1024;
+  static constexpr int B_STAT = 0, B_RFULL = 1, B_REMPTY = 1 + NSLOT, B_GFULL = 1 + 2 * NSLOT,
+                       B_TFULL = B_GFULL + 2, B_ACC = B_TFULL + 2, B_COUNT = B_ACC + 1;
+  static_assert(B_COUNT <= 32, "barrier storage");
+  static_assert(SMEM > 120 * 1024 && SMEM <= 227 * 1024, "one CTA per SM (512 TMEM columns)");
+};
+
+__device__ __forceinline__ float bneg_inf() { return __int_as_float(0xff800000); }
+
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+template <int MODE, bool IS_BF16>
+__global__ void __launch_bounds__(384, 1)
+bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_constant__ CUtensorMap tm_stat2,
+                 const __grid_constant__ CUtensorMap tm_str1, const __grid_constant__ CUtensorMap tm_str2,
+                 const AttnKParams p) {
+  using Cfg = BwdSm100Cfg;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t sStat = sbase + Cfg::OFF_STAT, sRing = sbase + Cfg::OFF_RING;
+  uint32_t* list = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_LIST);
+  const uint32_t bars = sbase + Cfg::OFF_BAR;
+  volatile int* misc = reinterpret_cast<volatile int*>(smem + Cfg::OFF_MISC);  // [0] tmem, [1] cnt, [4] abort
+  auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+
+  const int tid = threadIdx.x;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+  const int lane = tid & 31;
+  const MaskDesc& md = p.md;
+  const int off = p.Sk - p.Sq;
+  const int G = p.Hq / p.Hkv;
+
+  // ---- CTA coordinates ----
+  int b, hk, hq0, row0;  // row0: first key (DKDV) or first query (DQ) of the stationary tile
+  if (MODE == MODE_DKDV) {
+    b = blockIdx.z; hk = blockIdx.y; hq0 = hk * G; row0 = blockIdx.x * 128;
+  } else {
+    const int n_tiles = (p.Sq + 127) / 128;
+    b = blockIdx.z; hq0 = blockIdx.y; hk = hq0 / G; row0 = (n_tiles - 1 - (int)blockIdx.x) * 128;
+  }
+  const int bh_mask = md.ncols ? ((md.mask_B == 1 ? 0 : b) * md.Hm + hq0 / (p.Hq / md.Hm)) : 0;
+  const int n_heads = (MODE == MODE_DKDV) ? G : 1;
+
+  if (tid == 0) misc[4] = 0;
+  if (warp == 8 && lane == 0) {
+    mbar_init(bar(Cfg::B_STAT), 1);
+    for (int i = 0; i < Cfg::NSLOT; ++i) {
+      mbar_init(bar(Cfg::B_RFULL + i), MODE == MODE_DQ ? 33 : 1);
+      mbar_init(bar(Cfg::B_REMPTY + i), 1);
+    }
+    for (int h = 0; h < 2; ++h) { mbar_init(bar(Cfg::B_GFULL + h), 1); mbar_init(bar(Cfg::B_TFULL + h), 128); }
+    mbar_init(bar(Cfg::B_ACC), 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_stat1); tma_prefetch_desc(&tm_stat2);
+    tma_prefetch_desc(&tm_str1); tma_prefetch_desc(&tm_str2);
+  }
+  if (warp == 9) {
+    tmem_alloc(sbase + Cfg::OFF_MISC, 512);
+    tmem_relinquish();
+  }
+  if (warp == 10) {
+    int cnt = 0;
+    if (MODE == MODE_DKDV) {
+      // 64-query half tiles that see key tile n = row0/128, ascending
+      const int n = row0 / 128;
+      const int n_half = (p.Sq + 63) / 64;
+      int lo = 0;
+      if (md.causal) lo = max(0, (row0 - off) / 64);
+      for (int base = lo; base < n_half; base += 32) {
+        const int idx = base + lane;
+        uint32_t f = 0;
+        if (idx < n_half) f = tile_flags(md, bh_mask, n, idx * 64, min(idx * 64 + 64, p.Sq), 128);
+        const uint32_t bal = __ballot_sync(0xffffffffu, f != 0);
+        const int pos = cnt + __popc(bal & ((1u << lane) - 1u));
+        if (f && pos < Cfg::LIST_MAX) list[pos] = (uint32_t)idx | (f << 16);
+        cnt += __popc(bal);
+      }
+    } else {
+      // 64-key half tiles visible to query tile [row0, row0+128), right to left
+      const int me = min(row0 + 128, p.Sq);
+      const int n_half = (p.Sk + 63) / 64;
+      int hi = n_half;
+      if (md.causal) hi = max(0, min(n_half, (me + off + 63) / 64));
+      for (int base = hi - 1; base >= 0; base -= 32) {
+        const int idx = base - lane;
+        uint32_t f = 0;
+        if (idx >= 0) {
+          f = tile_flags(md, bh_mask, idx >> 1, row0, me, 128);
+          if (md.causal && idx * 64 > me - 1 + off) f = 0;
+        }
+        const uint32_t bal = __ballot_sync(0xffffffffu, f != 0);
+        const int pos = cnt + __popc(bal & ((1u << lane) - 1u));
+        if (f && pos < Cfg::LIST_MAX) list[pos] = (uint32_t)idx | (f << 16);
+        cnt += __popc(bal);
+      }
+    }
+    if (lane == 0) misc[1] = min(cnt, Cfg::LIST_MAX);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = (uint32_t)misc[0];
+  const int cnt = misc[1];
+  const int K_items = cnt * n_heads;
+  WaitCtx wc{misc + 4, global_timer_ns() + 2000000000ull};
+  // TMEM columns: G1_p at 64p, G2_p at 128+64p, accumulators at 256 (dV | dQ) and 384 (dK)
+  constexpr uint32_t C_G1 = 0, C_G2 = 128, C_ACC1 = 256, C_ACC2 = 384;
+
+  if (warp < 8) {
+    // =========================== compute warpgroups ===========================
+    setmaxnreg_inc<200>();
+    const int pz = warp >> 2;                    // item parity this warpgroup serves
+    const int r = tid & 127;                     // TMEM lane
+    const uint32_t lane_field = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tG1 = tmem + lane_field + C_G1 + 64u * pz;
+    const uint32_t tG2 = tmem + lane_field + C_G2 + 64u * pz;
+    const float scale_log2 = p.scale_log2;
+    bool ok = true;
+
+    // per-lane constants
+    int lts = INT_MAX, lte = INT_MAX, uts = 0, ute = 0;   // DKDV: bounds of key row0 + r
+    float lse2_row = 0.f, dps_row = 0.f;                   // DQ: statistics of query row0 + r
+    if (MODE == MODE_DKDV) {
+      const int j = row0 + r;
+      if (j >= p.Sk) { lts = 0; lte = INT_MAX; }
+      else if (md.ncols) {
+        const Bounds4 bd = load_bounds(md, md.mask + ((size_t)bh_mask * p.Sk + j) * md.ncols);
+        lts = bd.lts; lte = bd.lte; uts = bd.uts; ute = bd.ute;
+      }
+    } else {
+      const int i = row0 + r;
+      if (i < p.Sq) {
+        lse2_row = p.lse_log2[((int64_t)b * p.Hq + hq0) * p.Sq_r + i];
+        dps_row = p.dpsum[((int64_t)b * p.Hq + hq0) * p.Sq_r + i];
+      }
+    }
+
+    for (int k = pz; k < K_items && ok; k += 2) {
+      const uint32_t e = list[k % cnt];
+      const int idx = (int)(e & 0xFFFFu);
+      const uint32_t flags = e >> 16;
+      const int slot = k % Cfg::NSLOT;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_RFULL + slot), (uint32_t)(k / Cfg::NSLOT) & 1u, wc));
+      if (!ok) break;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_GFULL + pz), (uint32_t)(k >> 1) & 1u, wc));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sr[64], dr[64];
+      tmem_ld32(tG1, sr); tmem_ld32(tG1 + 32, sr + 32);
+      tmem_ld32(tG2, dr); tmem_ld32(tG2 + 32, dr + 32);
+      tc_wait_ld();
+      const uint8_t* aux = smem + Cfg::OFF_AUX + slot * Cfg::AUX_BYTES;
+      const uint32_t NEG = 0xff800000u;
+      uint32_t pk1[32], pk2[32];
+      if (MODE == MODE_DKDV) {
+        // columns are queries i0 + c; this lane is key j
+        const int i0 = idx * 64;
+        if (flags & ~FM_TF_ACTIVE) {
+          const int a0 = lts - i0, a1 = lte - i0, b0 = uts - i0, b1 = ute - i0;
+          const int cz = md.causal ? (row0 + r - off - i0) : INT_MIN;   // masked while c < cz
+#pragma unroll
+          for (int c = 0; c < 64; ++c)
+            if ((c >= a0 && c < a1) || (c >= b0 && c < b1) || c < cz) sr[c] = NEG;
+        }
+        const float4* st = reinterpret_cast<const float4*>(aux);
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4) {
+          const float4 l4 = st[c4], d4 = st[16 + c4];
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv4[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pe[4], de[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            pe[u] = fast_exp2(fmaf(__uint_as_float(sr[4 * c4 + u]), scale_log2, -lv[u]));
+            de[u] = pe[u] * (__uint_as_float(dr[4 * c4 + u]) - dv4[u]);
+          }
+          pk1[2 * c4] = pack2<IS_BF16>(pe[0], pe[1]); pk1[2 * c4 + 1] = pack2<IS_BF16>(pe[2], pe[3]);
+          pk2[2 * c4] = pack2<IS_BF16>(de[0], de[1]); pk2[2 * c4 + 1] = pack2<IS_BF16>(de[2], de[3]);
+        }
+        tmem_st32(tG1 + 32, pk1);
+        tmem_st32(tG2 + 32, pk2);
+      } else {
+        // columns are keys jh0 + c; this lane is query i
+        const int jh0 = idx * 64;
+        const int i = row0 + r;
+        if (flags & FM_TF_BOUNDS) {
+          const int4* bp = reinterpret_cast<const int4*>(aux);
+          if (md.ncols == 1) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int4 v = bp[j];
+              if (i >= v.x) sr[4 * j] = NEG;
+              if (i >= v.y) sr[4 * j + 1] = NEG;
+              if (i >= v.z) sr[4 * j + 2] = NEG;
+              if (i >= v.w) sr[4 * j + 3] = NEG;
+            }
+          } else if (md.ncols == 2 && md.causal) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int4 v = bp[j];
+              if (i >= v.x && i < v.y) sr[2 * j] = NEG;
+              if (i >= v.z && i < v.w) sr[2 * j + 1] = NEG;
+            }
+          } else if (md.ncols == 2) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int4 v = bp[j];
+              if (i >= v.x || i < v.y) sr[2 * j] = NEG;
+              if (i >= v.z || i < v.w) sr[2 * j + 1] = NEG;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) {
+              const int4 v = bp[j];
+              if ((i >= v.x && i < v.y) || (i >= v.z && i < v.w)) sr[j] = NEG;
+            }
+          }
+        }
+        if (flags & (FM_TF_CAUSAL | FM_TF_RAGGED)) {
+          int jmax = p.Sk - 1 - jh0;
+          if (md.causal) jmax = min(jmax, i + off - jh0);
+#pragma unroll
+          for (int c = 0; c < 64; ++c)
+            if (c > jmax) sr[c] = NEG;
+        }
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), scale_log2, -lse2_row));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), scale_log2, -lse2_row));
+          pk2[c] = pack2<IS_BF16>(p0 * (__uint_as_float(dr[2 * c]) - dps_row),
+                                  p1 * (__uint_as_float(dr[2 * c + 1]) - dps_row));
+        }
+        tmem_st32(tG2 + 32, pk2);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(Cfg::B_TFULL + pz));
+    }
+
+    // ---- epilogue ----
+    if (ok && K_items > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_ACC), 0u, wc));
+      tc_fence_after();
+    }
+    if (ok) {
+      if (MODE == MODE_DKDV) {
+        // warpgroup 0: dK (scaled) staged in the K tile; warpgroup 1: dV staged in the V tile
+        const uint32_t tA = tmem + lane_field + (pz == 0 ? C_ACC2 : C_ACC1);
+        const float mul = pz == 0 ? p.scale : 1.f;
+        uint8_t* stage = smem + Cfg::OFF_STAT + pz * Cfg::TILE_BYTES;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t orr[32];
+          if (K_items > 0) { tmem_ld32(tA + 32 * c, orr); tc_wait_ld(); }
+          else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) orr[j] = 0u;
+          }
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 v;
+            v.x = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 0]) * mul, __uint_as_float(orr[8 * q4 + 1]) * mul);
+            v.y = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 2]) * mul, __uint_as_float(orr[8 * q4 + 3]) * mul);
+            v.z = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 4]) * mul, __uint_as_float(orr[8 * q4 + 5]) * mul);
+            v.w = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 6]) * mul, __uint_as_float(orr[8 * q4 + 7]) * mul);
+            const int chunk = 4 * c + q4;
+            *reinterpret_cast<uint4*>(stage + r * 256 + ((chunk ^ (r & 15)) << 4)) = v;
+          }
+        }
+        __syncwarp();   // each warp stores the 32 rows it staged itself: no cross-warp dependency
+        uint16_t* gout = pz == 0
+            ? reinterpret_cast<uint16_t*>(p.dk) + b * p.dk_b + (int64_t)row0 * p.dk_s + hk * p.dk_h
+            : reinterpret_cast<uint16_t*>(p.dv) + b * p.dv_b + (int64_t)row0 * p.dv_s + hk * p.dv_h;
+        const int64_t ld = pz == 0 ? p.dk_s : p.dv_s;
+        const int wrow = (warp & 3) * 32;
+#pragma unroll 4
+        for (int x = lane; x < 32 * 16; x += 32) {
+          const int rr = wrow + (x >> 4), cc = x & 15;
+          if (row0 + rr < p.Sk)
+            *reinterpret_cast<uint4*>(gout + (int64_t)rr * ld + cc * 8) =
+                *reinterpret_cast<const uint4*>(stage + rr * 256 + ((cc ^ (rr & 15)) << 4));
+        }
+      } else {
+        // both warpgroups: dQ columns [64 pz, 64 pz + 64), staged in the Q tile
+        const uint32_t tA = tmem + lane_field + C_ACC1 + 64u * pz;
+        uint8_t* stage = smem + Cfg::OFF_STAT;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t orr[32];
+          if (K_items > 0) { tmem_ld32(tA + 32 * c, orr); tc_wait_ld(); }
+          else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) orr[j] = 0u;
+          }
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 v;
+            v.x = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 0]) * p.scale, __uint_as_float(orr[8 * q4 + 1]) * p.scale);
+            v.y = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 2]) * p.scale, __uint_as_float(orr[8 * q4 + 3]) * p.scale);
+            v.z = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 4]) * p.scale, __uint_as_float(orr[8 * q4 + 5]) * p.scale);
+            v.w = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 6]) * p.scale, __uint_as_float(orr[8 * q4 + 7]) * p.scale);
+            const int chunk = 8 * pz + 4 * c + q4;
+            *reinterpret_cast<uint4*>(stage + r * 256 + ((chunk ^ (r & 15)) << 4)) = v;
+          }
+        }
+        __syncwarp();   // warp-local transpose through the staging tile
+        uint16_t* gout = reinterpret_cast<uint16_t*>(p.dq) + b * p.dq_b + (int64_t)row0 * p.dq_s + hq0 * p.dq_h;
+        const int wrow = (warp & 3) * 32;
+#pragma unroll 4
+        for (int x = lane; x < 32 * 8; x += 32) {
+          const int rr = wrow + (x >> 3), cc = 8 * pz + (x & 7);
+          if (row0 + rr < p.Sq)
+            *reinterpret_cast<uint4*>(gout + (int64_t)rr * p.dq_s + cc * 8) =
+                *reinterpret_cast<const uint4*>(stage + rr * 256 + ((cc ^ (rr & 15)) << 4));
+        }
+      }
+    }
+  } else {
+    setmaxnreg_dec<64>();
+    if (warp == 8) {
+      // =========================== producer ===========================
+      if (lane == 0 && K_items > 0) {
+        mbar_arrive_expect_tx(bar(Cfg::B_STAT), 2 * Cfg::TILE_BYTES);
+        const int hs = (MODE == MODE_DKDV) ? hk : hq0;
+        for (int dc = 0; dc < 2; ++dc) {
+          tma_load_4d(sStat + dc * Cfg::SUB128, &tm_stat1, bar(Cfg::B_STAT), dc * 64, hs, row0, b);
+          tma_load_4d(sStat + Cfg::TILE_BYTES + dc * Cfg::SUB128, &tm_stat2, bar(Cfg::B_STAT), dc * 64, hs, row0, b);
+        }
+      }
+      bool ok = true;
+      for (int k = 0; k < K_items && ok; ++k) {
+        const uint32_t e = list[k % cnt];
+        const int idx = (int)(e & 0xFFFFu);
+        const uint32_t flags = e >> 16;
+        const int slot = k % Cfg::NSLOT;
+        const uint32_t par = ((uint32_t)(k / Cfg::NSLOT) & 1u) ^ 1u;
+        const int hstr = (MODE == MODE_DKDV) ? hq0 + k / cnt : hk;
+        if (MODE == MODE_DQ) {
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_REMPTY + slot), par, wc));
+        } else {
+          if (lane == 0) ok = mbar_wait(bar(Cfg::B_REMPTY + slot), par, wc);
+          ok = __all_sync(0xffffffffu, ok);
+        }
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t dst = sRing + slot * Cfg::SLOT_BYTES;
+          const uint32_t fb = bar(Cfg::B_RFULL + slot);
+          mbar_arrive_expect_tx(fb, Cfg::SLOT_BYTES + (MODE == MODE_DKDV ? 512 : 0));
+          for (int dc = 0; dc < 2; ++dc) {
+            tma_load_4d(dst + dc * Cfg::SUB64, &tm_str1, fb, dc * 64, hstr, idx * 64, b);
+            tma_load_4d(dst + Cfg::HALF_BYTES + dc * Cfg::SUB64, &tm_str2, fb, dc * 64, hstr, idx * 64, b);
+          }
+          if (MODE == MODE_DKDV) {
+            const int64_t at = ((int64_t)b * p.Hq + hstr) * p.Sq_r + idx * 64;
+            const uint32_t ax = sbase + Cfg::OFF_AUX + slot * Cfg::AUX_BYTES;
+            bulk_copy_g2s(ax, p.lse_log2 + at, 256, fb);
+            bulk_copy_g2s(ax + 256, p.dpsum + at, 256, fb);
+          }
+        }
+        if (MODE == MODE_DQ) {
+          if (flags & FM_TF_BOUNDS) {
+            int* dst = reinterpret_cast<int*>(smem + Cfg::OFF_AUX + slot * Cfg::AUX_BYTES);
+            const int jh0 = idx * 64;
+            const int32_t* src = md.mask + ((size_t)bh_mask * p.Sk + jh0) * md.ncols;
+            const int valid = min(64, p.Sk - jh0) * md.ncols;
+            for (int x = lane; x < 64 * md.ncols; x += 32) dst[x] = x < valid ? __ldg(src + x) : 0;
+          }
+          mbar_arrive(bar(Cfg::B_RFULL + slot));
+        }
+      }
+    } else if (warp == 9) {
+      // =========================== UMMA issuer ===========================
+      if (lane == 0 && K_items > 0) {
+        constexpr uint32_t idesc_g = make_idesc(IS_BF16, 128, 64, 0, 0);
+        constexpr uint32_t idesc_acc = make_idesc(IS_BF16, 128, 128, 0, 1);
+        bool ok = mbar_wait(bar(Cfg::B_STAT), 0u, wc);
+        auto issue_g = [&](int k) {
+          const int slot = k % Cfg::NSLOT, pz = k & 1;
+          ok = ok && mbar_wait(bar(Cfg::B_RFULL + slot), (uint32_t)(k / Cfg::NSLOT) & 1u, wc);
+          if (!ok) return;
+          tc_fence_after();
+          const uint32_t bsl = sRing + slot * Cfg::SLOT_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t oa = (uint32_t)(kk >> 2) * Cfg::SUB128 + (uint32_t)(kk & 3) * 32u;
+            const uint32_t ob = (uint32_t)(kk >> 2) * Cfg::SUB64 + (uint32_t)(kk & 3) * 32u;
+            umma_ss(tmem + C_G1 + 64u * pz, make_sdesc(sStat + oa, 16, 1024), make_sdesc(bsl + ob, 16, 1024),
+                    idesc_g, kk > 0 ? 1u : 0u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t oa = (uint32_t)(kk >> 2) * Cfg::SUB128 + (uint32_t)(kk & 3) * 32u;
+            const uint32_t ob = (uint32_t)(kk >> 2) * Cfg::SUB64 + (uint32_t)(kk & 3) * 32u;
+            umma_ss(tmem + C_G2 + 64u * pz, make_sdesc(sStat + Cfg::TILE_BYTES + oa, 16, 1024),
+                    make_sdesc(bsl + Cfg::HALF_BYTES + ob, 16, 1024), idesc_g, kk > 0 ? 1u : 0u);
+          }
+          tc_commit(bar(Cfg::B_GFULL + pz));
+        };
+        issue_g(0);
+        if (K_items > 1) issue_g(1);
+        for (int k = 0; k < K_items && ok; ++k) {
+          const int slot = k % Cfg::NSLOT, pz = k & 1;
+          ok = mbar_wait(bar(Cfg::B_TFULL + pz), (uint32_t)(k >> 1) & 1u, wc);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t bsl = sRing + slot * Cfg::SLOT_BYTES;
+          const uint32_t acc_on = k > 0 ? 1u : 0u;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            if (MODE == MODE_DKDV) {
+              // dV += P^T dO (streamed operand 2), dK += dS^T Q (streamed operand 1)
+              umma_ts(tmem + C_ACC1, tmem + C_G1 + 64u * pz + 32u + 8u * kk,
+                      make_sdesc(bsl + Cfg::HALF_BYTES + kk * 2048u, Cfg::SUB64, 1024), idesc_acc,
+                      (acc_on || kk > 0) ? 1u : 0u);
+              umma_ts(tmem + C_ACC2, tmem + C_G2 + 64u * pz + 32u + 8u * kk,
+                      make_sdesc(bsl + kk * 2048u, Cfg::SUB64, 1024), idesc_acc, (acc_on || kk > 0) ? 1u : 0u);
+            } else {
+              // dQ += dS K (streamed operand 1)
+              umma_ts(tmem + C_ACC1, tmem + C_G2 + 64u * pz + 32u + 8u * kk,
+                      make_sdesc(bsl + kk * 2048u, Cfg::SUB64, 1024), idesc_acc, (acc_on || kk > 0) ? 1u : 0u);
+            }
+          }
+          tc_commit(bar(Cfg::B_REMPTY + slot));
+          if (k + 2 < K_items) issue_g(k + 2);
+        }
+        if (ok) tc_commit(bar(Cfg::B_ACC));
+      }
+      __syncwarp();
+    }
+  }
+
+  // =========================== teardown ===========================
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (misc[4] != 0) {
+    const uint64_t t_end = global_timer_ns() + 200000ull;
+    while (global_timer_ns() < t_end) __nanosleep(1000);
+    if (tid == 0) atomicExch(&g_bwd_status, FM_ERR_TIMEOUT);
+  }
+  if (warp == 9) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------
+// host
+// ---------------------------------------------------------------------------
+bool bwd_sm100_supported(const fm_attn_args* a) {
+  if (!(a->d == 128 && a->dv == 128)) return false;
+  if (((uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v | (uintptr_t)a->d_o) & 15) return false;
+  return true;
+}
+
+template <bool IS_BF16>
+static int launch_bwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
+  using Cfg = BwdSm100Cfg;
+  FM_REQUIRE((a->Sq + 63) / 64 <= Cfg::LIST_MAX && (a->Sk + 63) / 64 <= Cfg::LIST_MAX, FM_ERR_UNSUPPORTED,
+             "backward: Sq=%d / Sk=%d exceed the %d rows this kernel variant indexes", a->Sq, a->Sk,
+             Cfg::LIST_MAX * 64);
+  CUtensorMap q128, do128, k128, v128, q64, do64, k64, v64;
+  int rc;
+#define FM_TMAP(out, ptr, S, H, D, st, rows)                                                          \
+  if ((rc = make_bshd_tmap(&out, ptr, a->dtype, a->B, S, H, D, st[0], st[1], st[2], rows))) return rc;
+  FM_TMAP(k128, a->k, a->Sk, a->Hkv, a->d, a->k_stride, 128)
+  FM_TMAP(v128, a->v, a->Sk, a->Hkv, a->dv, a->v_stride, 128)
+  FM_TMAP(q64, a->q, a->Sq, a->Hq, a->d, a->q_stride, 64)
+  FM_TMAP(do64, a->d_o, a->Sq, a->Hq, a->dv, a->do_stride, 64)
+  FM_TMAP(q128, a->q, a->Sq, a->Hq, a->d, a->q_stride, 128)
+  FM_TMAP(do128, a->d_o, a->Sq, a->Hq, a->dv, a->do_stride, 128)
+  FM_TMAP(k64, a->k, a->Sk, a->Hkv, a->d, a->k_stride, 64)
+  FM_TMAP(v64, a->v, a->Sk, a->Hkv, a->dv, a->v_stride, 64)
+#undef FM_TMAP
+  auto k1 = bwd_sm100_kernel<MODE_DKDV, IS_BF16>;
+  auto k2 = bwd_sm100_kernel<MODE_DQ, IS_BF16>;
+  FM_CUDA_TRY(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+  FM_CUDA_TRY(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+  k1<<<dim3((p.Sk + 127) / 128, p.Hkv, p.B), Cfg::NTHREADS, Cfg::SMEM, s>>>(k128, v128, q64, do64, p);
+  FM_CUDA_TRY(cudaGetLastError());
+  k2<<<dim3((p.Sq + 127) / 128, p.Hq, p.B), Cfg::NTHREADS, Cfg::SMEM, s>>>(q128, do128, k64, v64, p);
+  FM_CUDA_TRY(cudaGetLastError());
+  return FM_OK;
+}
+
+int bwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
+  return a->dtype == FM_DTYPE_BF16 ? launch_bwd_sm100<true>(p, a, s) : launch_bwd_sm100<false>(p, a, s);
+}
+
+int bwd_sm100_status(int* out, bool reset) {
+  int v = 0;
+  FM_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_bwd_status, sizeof(int)));
+  if (reset && v != 0) {
+    const int z = 0;
+    FM_CUDA_TRY(cudaMemcpyToSymbol(g_bwd_status, &z, sizeof(int)));
+  }
+  *out = v;
+  return FM_OK;
+}
+
+}  // namespace fm

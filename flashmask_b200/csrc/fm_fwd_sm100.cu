@@ -291,12 +291,13 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
       if (row < p.Sq)
         p.lse[((int64_t)b * p.Hq + hq) * p.Sq + row] = l_tot > 0.f ? (m_fin + log2f(l_tot)) * kLn2 : neg_inf();
-      named_bar_sync(1 + s, 128);
+      __syncwarp();   // each warp stores the 32 rows it staged itself: no cross-warp dependency
       uint16_t* go = reinterpret_cast<uint16_t*>(p.o) + b * p.o_b + (int64_t)(ms + 128 * s) * p.o_s + hq * p.o_h;
       constexpr int CH = DV / 8;
+      const int wrow = (warp & 3) * 32;
 #pragma unroll 4
-      for (int idx = r; idx < 128 * CH; idx += 128) {
-        const int rr = idx / CH, cc = idx % CH;
+      for (int idx = lane; idx < 32 * CH; idx += 32) {
+        const int rr = wrow + idx / CH, cc = idx % CH;
         if (ms + 128 * s + rr < p.Sq) {
           const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * (DV * 2) + ((cc ^ (rr & (CH - 1))) << 4));
           *reinterpret_cast<uint4*>(go + (int64_t)rr * p.o_s + cc * 8) = v;

@@ -133,7 +133,7 @@ def _check_shapes(q, k, v, idx, causal):
         assert idx.dim() == 4, "startend_row_indices must be [B, Hm, Sk, n]"
         assert idx.shape[0] in (B, 1), "startend_row_indices batch must match q"
         assert idx.shape[2] == Sk, "startend_row_indices seqlen must match k"
-        assert idx.shape[1] in (1, Hkv, Hq), "startend_row_indices heads must be 1 or num kv heads"
+        assert idx.shape[1] in (1, Hkv), "startend_row_indices heads must be 1 or num kv heads"
         if causal:
             assert idx.shape[-1] in (1, 2), "causal masks carry 1 or 2 bounds per column"
         else:

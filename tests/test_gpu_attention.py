@@ -17,15 +17,18 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(params=["sm100", "mma"])
 def fwd_variant(request):
-    """d = dv = 128 has two forward kernels: the tcgen05 one (default) and the
-    warp-MMA one; FLASHMASK_B200_FWD selects per call."""
-    old = os.environ.get("FLASHMASK_B200_FWD")
-    os.environ["FLASHMASK_B200_FWD"] = request.param
+    """d = dv = 128 has two kernel families: the tcgen05 ones (default) and the
+    warp-MMA ones; FLASHMASK_B200_FWD / FLASHMASK_B200_BWD select per call."""
+    names = ("FLASHMASK_B200_FWD", "FLASHMASK_B200_BWD")
+    old = {n: os.environ.get(n) for n in names}
+    for n in names:
+        os.environ[n] = request.param
     yield request.param
-    if old is None:
-        os.environ.pop("FLASHMASK_B200_FWD", None)
-    else:
-        os.environ["FLASHMASK_B200_FWD"] = old
+    for n in names:
+        if old[n] is None:
+            os.environ.pop(n, None)
+        else:
+            os.environ[n] = old[n]
 
 
 def _kernel_status():
@@ -176,7 +179,7 @@ def test_against_reference_golden(path):
         assert err < 0.15, (n, err)
 
 
-def test_deterministic_bitwise():
+def test_deterministic_bitwise(fwd_variant):
     idx_np, causal = _mask("causal_doc", 2, 512, 512, 21)
     q, k, v, do, s = make_inputs(2, 512, 512, 8, 2, 128, 128, 21, sink=True)
     idx = torch.from_numpy(np.ascontiguousarray(idx_np).copy()).cuda()
@@ -187,7 +190,7 @@ def test_deterministic_bitwise():
             assert torch.equal(a[n], b[n]), n
 
 
-def test_layout_invariance():
+def test_layout_invariance(fwd_variant):
     """Contiguous vs permuted storage of q/k/v give bitwise equal results
     (reference: tests/torch/test_flashmask.py:354-396)."""
     idx_np, causal = _mask("causal_doc", 1, 256, 256, 5)
