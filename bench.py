@@ -129,6 +129,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -270,27 +271,30 @@ def main():
     h2d = sum(t_.numel() * t_.element_size() for t_ in host.values()) + \
         (idx_host.numel() * 4 if idx_host is not None else 0)
     d2h = sum(t_.numel() * t_.element_size() for t_ in res.values())
-    for _ in range(2):
-        step_e2e()
-    barrier()
-    e_steps = max(3, args.steps // 2)
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(e_steps):
-        step_e2e()
-    b.record()
-    barrier()
-    te = torch.tensor([a.elapsed_time(b)], device=dev)
-    if world > 1:
-        torch.distributed.all_reduce(te, op=torch.distributed.ReduceOp.MAX)
-    e2e_val = world * (fwd_flops + bwd_flops) / (te.item() / e_steps * 1e-3) / 1e12
+    e2e = None
+    if not args.no_e2e:
+        for _ in range(2):
+            step_e2e()
+        barrier()
+        e_steps = max(3, args.steps // 2)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(e_steps):
+            step_e2e()
+        b.record()
+        barrier()
+        te = torch.tensor([a.elapsed_time(b)], device=dev)
+        if world > 1:
+            torch.distributed.all_reduce(te, op=torch.distributed.ReduceOp.MAX)
+        e2e_val = world * (fwd_flops + bwd_flops) / (te.item() / e_steps * 1e-3) / 1e12
+        e2e = {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": te.item() / e_steps}
 
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": config, "clocks": clocks,
-            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": te.item() / e_steps},
+            "e2e": e2e,
             "gpu_launches": launches_per_step * args.steps, "roofline": roofline,
             "frac_of_peak_fwd_bwd": value / world / peak_tf,
             "tokens_per_s": world * w.B * w.Sq / (ms_step * 1e-3)}
