@@ -56,6 +56,19 @@ SIGNATURES = {
     "fm_bwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "fm_kernel_status": (C.c_int, [C.POINTER(C.c_int), C.c_int]),
     "fm_bwd_static_scratch": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
+    "fm_cp_chunk_workload": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "fm_cp_partition_heap": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "fm_cp_rerank": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                               C.c_int, C.c_int, C.c_void_p]),
+    "fm_cp_localize": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
+    "fm_cp_shard_visible": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                      C.c_int, C.c_void_p, C.c_void_p]),
+    "fm_cp_merge_partial": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                      C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "fm_cp_accumulate": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
+    "fm_cp_cast": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
+    "fm_cp_reduce_partials": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_void_p, C.c_int64, C.c_int,
+                                        C.c_void_p]),
 }
 
 _lib = None

@@ -168,6 +168,61 @@ FM_API int fm_kernel_status(int* status, int reset);
 FM_API size_t fm_bwd_workspace_bytes(const fm_attn_args* args);
 FM_API int fm_bwd(const fm_attn_args* args, void* stream);
 
+/* ------------------------------------------------------------------------
+ * Context parallel (sequence sharded over ranks)
+ * ------------------------------------------------------------------------ */
+
+/* Workload per balance chunk: out[h, c] = {sum over batch and over the 128-row
+ * blocks of chunk c of valid_cnt, c}; out is int32 [Hm, ceil(Tq/blocks_per_chunk), 2].
+ * `valid_cnt` comes from fm_mask_prepare(causal=0, tile 128x128).
+ * Replaces get_q_workload + reduce_workload_kernel
+ * (flashmask/cp_balance/cp_balance.py:11-93, csrc/cp_balance_bridge.cu:74-151);
+ * only real K blocks are counted (the reference also walks the uninitialised
+ * pad entries of its scan output, which is only well defined when S % 512 == 0,
+ * where both agree). */
+FM_API int fm_cp_chunk_workload(const int32_t* valid_cnt, int B, int Hm, int Tq, int blocks_per_chunk,
+                                int32_t* out, void* stream);
+
+/* LPT heap partition of n weighted tasks into n_buckets buckets of capacity
+ * n / n_buckets (HOST pointers).  bucket_of[t] = bucket of task t.
+ * Replaces assign_tasks_heap (flashmask/cp_balance/cp_balance.py:96-174). */
+FM_API int fm_cp_partition_heap(const int32_t* weights, int n, int n_buckets, int32_t* bucket_of);
+
+/* Gather the key axis of the mask into chunk order `chunk_idx`:
+ * out[b,h,c*C + r,:] = mask[b,h,chunk_idx[c]*C + r,:].
+ * Replaces indices_rerank_kernel (csrc/cp_balance_bridge.cu:185-216). */
+FM_API int fm_cp_rerank(const int32_t* mask, const int32_t* chunk_idx, int32_t* out, int B, int H, int S,
+                        int D, int n_chunks, int chunk_size, void* stream);
+
+/* Map global row bounds into the row space of the rank that owns chunks
+ * `local_chunk_idx` (n elements of `mask`, any shape).
+ * Replaces indices_to_chunks_kernel (csrc/cp_balance_bridge.cu:153-183). */
+FM_API int fm_cp_localize(const int32_t* mask, const int32_t* local_chunk_idx, int32_t* out, int64_t n,
+                          int n_local, int chunk_size, void* stream);
+
+/* out[(b*Hm+h), s] = unmasked pairs between the Sq local rows and key shard s
+ * (Sk / n_shards columns each): a rank needs shard s iff the sum over (b,h) is
+ * non-zero.  Plays the role of ChunkMaskKernel
+ * (flashmask/overlap/csrc/distributed/remote_get_kernel.cuh:45-71). */
+FM_API int fm_cp_shard_visible(const int32_t* mask, int B, int Hm, int Sq, int Sk, int ncols, int causal,
+                               int n_shards, int64_t* out, void* stream);
+
+/* Running log-sum-exp merge of forward partials (acc fp32 [B,S,H,dv],
+ * lse_run fp32 [B,H,S]) with (o_s 16-bit [B,S,H,dv], lse_s): first != 0
+ * initialises.  fm_cp_cast rounds the accumulator to the 16-bit output.
+ * No reference counterpart: the reference gathers K/V and runs one kernel
+ * (tests/torch/distributed/all_gather_flashmask.py:29-111). */
+FM_API int fm_cp_merge_partial(float* acc, float* lse_run, const void* o_s, const float* lse_s, int B, int S,
+                               int H, int dv, int dtype, int first, void* stream);
+FM_API int fm_cp_accumulate(float* acc, const void* x, int64_t n, int dtype, int first, void* stream);
+FM_API int fm_cp_cast(const float* acc, void* out, int64_t n, int dtype, void* stream);
+
+/* out = round(sum_i fp32(parts[i])) in index order (deterministic); parts is
+ * a HOST array of n_parts <= 64 device pointers to 16-bit arrays of n elements.
+ * Replaces ReducedKdVKernel (flashmask/overlap/csrc/distributed/dk_dv_reduce_bf16.cuh:58-168). */
+FM_API int fm_cp_reduce_partials(const void* const* parts, int n_parts, void* out, int64_t n, int dtype,
+                                 void* stream);
+
 /*
  * Backward without any allocation, for callers that cannot provide device
  * memory of their own at call time: code running under a memory pool that is
