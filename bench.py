@@ -121,6 +121,117 @@ def time_cpu(step, flops, steps, warmup):
 
 
 # ---------------------------------------------------------------------------
+# context-parallel leg (N > 1): 128K-token causal-document mask, sequence sharded
+# ---------------------------------------------------------------------------
+def run_cp(args, rank, local_rank, world):
+    import torch.distributed as dist
+    import flashmask_b200 as fm
+    from flashmask_b200 import cp_balance, workloads as W
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    name = args.workload or "cp_causal_doc_128k"
+    w = W.make_workload(name)
+    chunk = 2048
+    idx = torch.from_numpy(w.idx).to(dev)
+    t0 = time.perf_counter()
+    local_mask, buckets = cp_balance.balance_flashmask_input(idx, world, rank, balance_chunk_size=chunk)
+    torch.cuda.synchronize()
+    partition_ms = (time.perf_counter() - t0) * 1e3
+    loads = [sum(x for x, _ in b) for b in buckets]
+    S_local = w.Sq // world
+    g = torch.Generator().manual_seed(w.seed + rank)
+    host = {n_: torch.randn(w.B, S_local, h, dd, generator=g).to(torch.bfloat16).pin_memory()
+            for n_, h, dd in (("q", w.Hq, w.d), ("k", w.Hkv, w.d), ("v", w.Hkv, w.dv), ("do", w.Hq, w.dv))}
+    q, k, v, do = (host[n_].to(dev) for n_ in ("q", "k", "v", "do"))
+    fwd_flops, bwd_flops = w.flops()
+    group = dist.group.WORLD
+
+    def step(qd, kd, vd, dod):
+        qd.requires_grad_(True); kd.requires_grad_(True); vd.requires_grad_(True)
+        o = fm.flashmask_attention(qd, kd, vd, local_mask, causal=False, group=group, deterministic=True)
+        o.backward(dod)
+        return o, qd.grad, kd.grad, vd.grad
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def fresh():
+        return q.detach().clone(), k.detach().clone(), v.detach().clone(), do
+
+    for _ in range(max(3, args.warmup)):
+        step(*fresh())
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ins = [fresh() for _ in range(args.steps)]
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        step(*ins[i])
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = t.item() / args.steps
+    value = (fwd_flops + bwd_flops) / (ms_step * 1e-3) / 1e12
+
+    e2e = None
+    if not args.no_e2e:
+        res = {n_: torch.empty_like(host[n_]).pin_memory() for n_ in ("q", "k", "v", "do")}
+
+        def step_e2e():
+            o, dq, dk, dv = step(*(host[n_].to(dev, non_blocking=True) for n_ in ("q", "k", "v", "do")))
+            res["do"].copy_(o.detach(), non_blocking=True); res["q"].copy_(dq, non_blocking=True)
+            res["k"].copy_(dk, non_blocking=True); res["v"].copy_(dv, non_blocking=True)
+        for _ in range(2):
+            step_e2e()
+        barrier()
+        n_e = max(3, args.steps // 2)
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n_e):
+            step_e2e()
+        b_.record()
+        barrier()
+        te = torch.tensor([a.elapsed_time(b_)], device=dev)
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        nbytes = sum(x.numel() * x.element_size() for x in host.values())
+        e2e = {"value": (fwd_flops + bwd_flops) / (te.item() / n_e * 1e-3) / 1e12, "unit": UNIT,
+               "h2d_bytes_per_step": nbytes * world, "d2h_bytes_per_step": nbytes * world,
+               "ms_per_step": te.item() / n_e}
+    from flashmask_b200 import cp as cpmod
+    n_needed = int(cpmod.shard_need_row(local_mask, S_local, False, world).sum().item())
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak_tf = peaks.get("bf16_tflops_sustained") or 1400.0
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{name}: B={w.B} Hq={w.Hq} Hkv={w.Hkv} S={w.Sq} d={w.d} causal-document mask "
+                                   f"(heavy-tailed lognormal docs) in the non-causal 2-column form, sequence sharded "
+                                   f"over {world} ranks by the mask-aware partitioner ({chunk}-row chunks)",
+                       "l2": "per-rank tensors exceed the 126 MB L2; no flush between steps",
+                       "mask_sparsity": round(w.sparsity(), 4), "parallelism": f"cp{world}",
+                       "partition_ms": partition_ms, "rank_loads": loads},
+            "clocks": clocks, "e2e": e2e,
+            "gpu_launches": args.steps * (8 * n_needed + 4), "tokens_per_s": w.B * w.Sq / (ms_step * 1e-3),
+            "roofline": {"bound": "tensor", "kernel": "fwd + bwd tcgen05 kernels over all ring steps (aggregate)",
+                         "achieved": value / world, "peak": peak_tf, "unit": "TFLOP/s",
+                         "frac": value / world / peak_tf, "peak_source": "measured (sustained cuBLAS bf16)",
+                         "traffic": None}}
+    if rank == 0:
+        print(json.dumps(line))
+    dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -161,12 +272,12 @@ def main():
         print(json.dumps(line))
         return
 
+    if world > 1:
+        return run_cp(args, rank, local_rank, world)
+
     import flashmask_b200 as fm
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
 
     g = torch.Generator().manual_seed(w.seed + rank)
     host = {
@@ -298,6 +409,23 @@ def main():
             "gpu_launches": launches_per_step * args.steps, "roofline": roofline,
             "frac_of_peak_fwd_bwd": value / world / peak_tf,
             "tokens_per_s": world * w.B * w.Sq / (ms_step * 1e-3)}
+    if world == 1 and not args.no_e2e and args.workload is None:
+        # the context-parallel workload on this one GPU: the N=1 point of the 128K scaling series
+        wc = W.make_workload("cp_causal_doc_128k")
+        gc = torch.Generator().manual_seed(wc.seed)
+        qc, kc, vc, doc = (torch.randn(wc.B, wc.Sq, h, wc.d, generator=gc).to(torch.bfloat16).to(dev)
+                           for h in (wc.Hq, wc.Hkv, wc.Hkv, wc.Hq))
+        idc = torch.from_numpy(wc.idx).to(dev)
+
+        def step_c():
+            o_, l_ = fm._flash_attn_fwd(qc, kc, vc, idc, causal=wc.causal)
+            return fm._flash_attn_bwd(qc, kc, vc, o_, doc, l_, idc, causal=wc.causal)
+        ms_c = timed(step_c, 5) if (step_c(), step_c(), step_c()) else 0.0
+        fc, bc = wc.flops()
+        line["cp_128k_single_gpu"] = {"ms_per_step": ms_c, "tokens_per_s": wc.B * wc.Sq / (ms_c * 1e-3),
+                                      "value": (fc + bc) / (ms_c * 1e-3) / 1e12, "unit": UNIT,
+                                      "mask_sparsity": round(wc.sparsity(), 4)}
+        del qc, kc, vc, doc
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cores = os.cpu_count() or 1
         torch.set_num_threads(cores)

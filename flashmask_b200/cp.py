@@ -229,9 +229,25 @@ def cp_backward(q, shards, out, dout, lse, local_mask, causal, softmax_scale, si
 # ---------------------------------------------------------------------------
 # autograd entry for real process groups
 # ---------------------------------------------------------------------------
+_PLAN_CACHE: Dict[tuple, CPPlan] = {}
+
+
 def build_plan(local_mask, Sq, causal, ex: TorchDistExchange) -> CPPlan:
+    """The need matrix costs one small all-gather and a device->host read; it
+    depends on the mask only, so it is kept per (mask storage, version, group)."""
+    key = None
+    if local_mask is not None:
+        key = (local_mask.data_ptr(), local_mask._version, tuple(local_mask.shape), Sq, ex.world, ex.rank,
+               id(ex.group))
+        if key in _PLAN_CACHE:
+            return _PLAN_CACHE[key]
     row = shard_need_row(local_mask, Sq, causal, ex.world)
-    return CPPlan(ex.world, ex.rank, ex.all_gather_need(row))
+    plan = CPPlan(ex.world, ex.rank, ex.all_gather_need(row))
+    if key is not None:
+        if len(_PLAN_CACHE) > 64:
+            _PLAN_CACHE.clear()
+        _PLAN_CACHE[key] = plan
+    return plan
 
 
 class _CPFunc(torch.autograd.Function):
