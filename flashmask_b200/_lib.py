@@ -55,6 +55,7 @@ SIGNATURES = {
     "fm_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(AttnArgs)]),
     "fm_bwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "fm_kernel_status": (C.c_int, [C.POINTER(C.c_int), C.c_int]),
+    "fm_selftest_bounded_wait": (C.c_int, [C.c_int, C.c_void_p]),
     "fm_bwd_static_scratch": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "fm_cp_chunk_workload": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "fm_cp_partition_heap": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),

@@ -9,15 +9,18 @@ its row bounds are local rows, and ``dk`` / ``dv`` come back reduced onto the
 owner of each shard.
 
 Schedule (one NVSwitch domain, every peer at full bandwidth): a rank pulls the
-shards it needs straight from their owners with NCCL send/recv pairs on a side
-stream, all posted up front into separate local buffers, and computes step by
-step as shards land (CUDA events gate each step).  A (rank, shard) pair whose
-tile of the mask holds no visible element is skipped: no transfer, no compute;
-all ranks derive the same need matrix from one small all-gather.  Forward
-partials are merged by log-sum-exp in fp32.  Backward sends the bf16 dK/dV
-partial of every needed shard to its owner, which sums all partials in rank
-order in fp32 and rounds once: bitwise reproducible.  Remote data is only ever
-consumed from local HBM.
+shards it needs straight from their owners with ONE grouped NCCL send/recv on a
+high-priority side stream, into one local K/V buffer that holds the other
+ranks' shards concatenated in rank order.  The forward is two attention calls
+whatever the group size: local queries x own shard (overlaps with the
+exchange) and local queries x that remote buffer (one launch; tile skipping
+drops shards, or parts of shards, that nothing sees), merged by log-sum-exp in
+fp32.  A (rank, shard) pair whose part of the mask holds no visible element is
+not transferred at all; all ranks derive the same need matrix from one small
+all-gather.  The backward runs the remote call first, sends each owner the
+bf16 dK/dV slice of its shard while the own-shard call runs, and every owner
+sums the contributions in rank order in fp32 and rounds once: bitwise
+reproducible.  Remote data is only ever consumed from local HBM.
 """
 from __future__ import annotations
 
@@ -31,8 +34,8 @@ import torch
 from . import _lib
 from .ops import _dtype_code, _flash_attn_bwd, _flash_attn_fwd, _stream
 
-__all__ = ["cp_flashmask_attention", "CPPlan", "TorchDistExchange", "InProcessExchange", "build_plan",
-           "cp_forward", "cp_backward"]
+__all__ = ["cp_flashmask_attention", "CPPlan", "TorchDistExchange", "RemoteKV", "build_plan", "cp_forward",
+           "emulate_cp", "shard_need_row"]
 
 
 # ---------------------------------------------------------------------------
@@ -69,10 +72,12 @@ def shard_need_row(local_mask: Optional[torch.Tensor], Sq: int, causal: bool, wo
 
 
 # ---------------------------------------------------------------------------
-# exchanges
+# exchange over a torch.distributed group
 # ---------------------------------------------------------------------------
 class TorchDistExchange:
-    """NCCL point-to-point over a torch.distributed group, on a side stream."""
+    """NCCL point-to-point over a torch.distributed group.  One grouped
+    send/recv (a single NCCL launch for all peers) per direction, issued from a
+    side stream before the compute it overlaps with is enqueued."""
 
     def __init__(self, group):
         import torch.distributed as dist
@@ -80,7 +85,7 @@ class TorchDistExchange:
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
-        self.comm_stream = torch.cuda.Stream() if torch.cuda.is_available() else None
+        self.comm_stream = torch.cuda.Stream(priority=-1) if torch.cuda.is_available() else None
 
     def _global(self, r):
         return self.dist.get_global_rank(self.group, r) if self.group is not None else r
@@ -90,48 +95,29 @@ class TorchDistExchange:
         self.dist.all_gather(rows, row, group=self.group)
         return [[bool(v) for v in r.cpu().tolist()] for r in rows]
 
-    def exchange(self, send: Dict[int, List[torch.Tensor]], recv: Dict[int, List[torch.Tensor]], order: List[int]):
-        """Post every send / recv on the side stream, paired per ring distance so
-        both ends issue matching operations in the same order.  Returns one CUDA
-        event per source rank in ``recv``."""
+    def exchange(self, send: Dict[int, List[torch.Tensor]], recv: Dict[int, List[torch.Tensor]]):
+        """Post all sends and receives as one group on the side stream (ordered
+        after the work already enqueued on the current stream).  Returns a CUDA
+        event that fires when every receive has landed."""
         dist = self.dist
         cur = torch.cuda.current_stream()
         self.comm_stream.wait_stream(cur)
-        events = {}
+        ev = torch.cuda.Event()
         with torch.cuda.stream(self.comm_stream):
-            for s in range(1, self.world):
-                src, dst = (self.rank - s) % self.world, (self.rank + s) % self.world
-                ops = []
-                if dst in send:
-                    ops += [dist.P2POp(dist.isend, t, self._global(dst), self.group) for t in send[dst]]
-                if src in recv:
-                    ops += [dist.P2POp(dist.irecv, t, self._global(src), self.group) for t in recv[src]]
-                if ops:
-                    for w in dist.batch_isend_irecv(ops):
-                        w.wait()
-                if src in recv:
-                    ev = torch.cuda.Event()
-                    ev.record(self.comm_stream)
-                    events[src] = ev
-                    for t in recv[src]:
-                        t.record_stream(cur)
-        for ts in send.values():
+            ops = []
+            for s in range(1, self.world):        # same peer order on every rank
+                for peer, table, fn in (((self.rank + s) % self.world, send, dist.isend),
+                                        ((self.rank - s) % self.world, recv, dist.irecv)):
+                    if peer in table:
+                        ops += [dist.P2POp(fn, t, self._global(peer), self.group) for t in table[peer]]
+            if ops:
+                for w in dist.batch_isend_irecv(ops):
+                    w.wait()
+            ev.record(self.comm_stream)
+        for ts in list(send.values()) + list(recv.values()):
             for t in ts:
                 t.record_stream(self.comm_stream)
-        return events
-
-    def finish(self):
-        torch.cuda.current_stream().wait_stream(self.comm_stream)
-
-
-class InProcessExchange:
-    """All ranks live in one process on one GPU (tests of the schedule and of the
-    merge / reduce arithmetic without a multi-GPU box).  Ranks are driven in
-    lock-step phases by ``emulate_cp``; an exchange is a dictionary lookup."""
-
-    def __init__(self, world: int):
-        self.world = world
-        self.mail: Dict[tuple, List[torch.Tensor]] = {}
+        return ev
 
 
 # ---------------------------------------------------------------------------
@@ -157,6 +143,7 @@ def _cast(acc, like):
 
 
 def _reduce_partials(parts: List[torch.Tensor]) -> torch.Tensor:
+    parts = [p.contiguous() for p in parts]
     out = torch.empty_like(parts[0])
     arr = (C.c_void_p * len(parts))(*[p.data_ptr() for p in parts])
     _lib.check(_lib.load().fm_cp_reduce_partials(arr, len(parts), out.data_ptr(), out.numel(),
@@ -164,66 +151,118 @@ def _reduce_partials(parts: List[torch.Tensor]) -> torch.Tensor:
     return out
 
 
-def _mask_slice(local_mask, owner, S_shard):
+# ---------------------------------------------------------------------------
+# per-rank forward / backward: two attention calls whatever the group size
+#   "own"    local queries x this rank's own K/V shard (needs no transfer and
+#            overlaps with the exchange)
+#   "remote" local queries x every other shard, concatenated in rank order in
+#            ONE K/V buffer with the matching mask columns: one launch, tile
+#            skipping takes care of shards (or parts of shards) nothing sees
+# ---------------------------------------------------------------------------
+def _remote_pos(owner: int, rank: int) -> int:
+    return owner if owner < rank else owner - 1
+
+
+def _split_mask(local_mask, rank, S_shard):
+    """(mask of the own shard's columns, mask of all other columns in rank order)."""
     if local_mask is None:
-        return None
-    return local_mask[:, :, owner * S_shard:(owner + 1) * S_shard, :].contiguous()
+        return None, None
+    lo, hi = rank * S_shard, (rank + 1) * S_shard
+    own = local_mask[:, :, lo:hi].contiguous()
+    rest = torch.cat([local_mask[:, :, :lo], local_mask[:, :, hi:]], dim=2).contiguous()
+    return own, rest
 
 
-# ---------------------------------------------------------------------------
-# per-rank forward / backward given the shards
-# ---------------------------------------------------------------------------
-def cp_forward(q, shards: Dict[int, tuple], local_mask, causal, softmax_scale, sink, plan: CPPlan,
-               events: Optional[Dict[int, torch.cuda.Event]] = None):
-    """Attend local ``q`` to every needed shard (own shard first, then the pulled
-    ones in ring-distance order) and merge.  Returns (out, lse)."""
-    B, Sq, Hq, d = q.shape
-    S_shard = shards[plan.rank][0].shape[1]
-    dv = shards[plan.rank][1].shape[-1]
+class RemoteKV:
+    """K/V of all other ranks' shards, concatenated along the sequence in rank
+    order.  For batch 1 the receive buffers ARE slices of the concatenation;
+    larger batches receive per owner and are copied into place."""
+
+    def __init__(self, k, v, world, rank):
+        B, S, H, d = k.shape
+        self.B, self.S, self.world, self.rank = B, S, world, rank
+        self.k = torch.empty((B, (world - 1) * S, H, d), dtype=k.dtype, device=k.device)
+        self.v = torch.empty((B, (world - 1) * S, v.shape[2], v.shape[3]), dtype=v.dtype, device=v.device)
+        self.tmp = {}
+
+    def recv_buffers(self, owner):
+        pos = _remote_pos(owner, self.rank)
+        ks, vs = self.k[:, pos * self.S:(pos + 1) * self.S], self.v[:, pos * self.S:(pos + 1) * self.S]
+        if self.B == 1:
+            return [ks, vs]
+        self.tmp[owner] = (torch.empty_like(ks.contiguous()), torch.empty_like(vs.contiguous()), ks, vs)
+        return list(self.tmp[owner][:2])
+
+    def finalize(self):
+        for tk, tv, ks, vs in self.tmp.values():
+            ks.copy_(tk); vs.copy_(tv)
+        self.tmp = {}
+
+    def slice_of(self, t, owner):
+        pos = _remote_pos(owner, self.rank)
+        return t[:, pos * self.S:(pos + 1) * self.S]
+
+
+def cp_forward(q, k, v, remote: Optional[RemoteKV], masks, softmax_scale, sink, plan: CPPlan, ready=None):
+    """Returns (out, lse).  ``ready``: CUDA event after which ``remote`` is complete."""
+    own_mask, rest_mask = masks
+    need_own = plan.need[plan.rank][plan.rank]
+    need_remote = remote is not None and len(plan.pulls()) > 0
+    parts = []
+    if need_own:
+        parts.append(_flash_attn_fwd(q, k, v, own_mask, softmax_scale=softmax_scale, causal=False,
+                                     learnable_sink=sink))
+    if need_remote:
+        if ready is not None:
+            torch.cuda.current_stream().wait_event(ready)
+        remote.finalize()
+        # the sink logit joins the softmax once: with the first partial only
+        parts.append(_flash_attn_fwd(q, remote.k, remote.v, rest_mask, softmax_scale=softmax_scale, causal=False,
+                                     learnable_sink=None if need_own else sink))
+    if len(parts) == 1:
+        return parts[0]
+    B, Sq, Hq, _ = q.shape
+    dv = v.shape[-1]
+    if not parts:
+        return (torch.zeros((B, Sq, Hq, dv), dtype=q.dtype, device=q.device),
+                torch.full((B, Hq, Sq), float("-inf"), dtype=torch.float32, device=q.device))
     acc = torch.empty((B, Sq, Hq, dv), dtype=torch.float32, device=q.device)
     lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device)
-    order = ([plan.rank] if plan.need[plan.rank][plan.rank] else []) + plan.pulls()
-    first = True
-    for o in order:
-        if events is not None and o in events:
-            torch.cuda.current_stream().wait_event(events[o])
-        k_o, v_o = shards[o]
-        # the sink logit joins the softmax once: with the first partial only
-        o_s, lse_s = _flash_attn_fwd(q, k_o, v_o, _mask_slice(local_mask, o, S_shard), softmax_scale=softmax_scale,
-                                     causal=False, learnable_sink=sink if first else None)
-        _merge(acc, lse, o_s, lse_s, first)
-        first = False
-    if first:  # nothing visible at all
-        acc.zero_()
-        lse.fill_(float("-inf"))
+    _merge(acc, lse, parts[0][0], parts[0][1], True)
+    _merge(acc, lse, parts[1][0], parts[1][1], False)
     return _cast(acc, q), lse
 
 
-def cp_backward(q, shards, out, dout, lse, local_mask, causal, softmax_scale, sink, deterministic, plan: CPPlan,
-                events=None):
-    """Returns (dq, partials, dsink): ``partials[o] = (dk_o, dv_o)`` are this
-    rank's contributions to the gradients of shard ``o``."""
-    S_shard = shards[plan.rank][0].shape[1]
-    order = ([plan.rank] if plan.need[plan.rank][plan.rank] else []) + plan.pulls()
-    dq_acc = torch.empty(q.shape, dtype=torch.float32, device=q.device)
-    partials = {}
-    dsink = None
-    first = True
-    for o in order:
-        if events is not None and o in events:
-            torch.cuda.current_stream().wait_event(events[o])
-        k_o, v_o = shards[o]
-        dq_s, dk_o, dv_o, ds = _flash_attn_bwd(q, k_o, v_o, out, dout, lse, _mask_slice(local_mask, o, S_shard),
-                                               softmax_scale=softmax_scale, causal=False,
-                                               learnable_sink=sink if first else None, deterministic=deterministic)
-        if first:
-            dsink = ds
-        _accumulate(dq_acc, dq_s, first)
-        partials[o] = (dk_o, dv_o)
-        first = False
-    if first:
-        dq_acc.zero_()
-    return _cast(dq_acc, q), partials, dsink
+def cp_backward_remote(q, remote, out, dout, lse, rest_mask, softmax_scale, deterministic):
+    """Gradients of the remote call: (dq_remote, dk_all_remote, dv_all_remote)."""
+    dq, dk, dv, _ = _flash_attn_bwd(q, remote.k, remote.v, out, dout, lse, rest_mask, softmax_scale=softmax_scale,
+                                    causal=False, deterministic=deterministic)
+    return dq, dk, dv
+
+
+def cp_backward_own(q, k, v, out, dout, lse, own_mask, softmax_scale, sink, deterministic):
+    return _flash_attn_bwd(q, k, v, out, dout, lse, own_mask, softmax_scale=softmax_scale, causal=False,
+                           learnable_sink=sink, deterministic=deterministic)
+
+
+def _sum_dq(dq_a, dq_b):
+    if dq_a is None:
+        return dq_b
+    if dq_b is None:
+        return dq_a
+    acc = torch.empty(dq_a.shape, dtype=torch.float32, device=dq_a.device)
+    _accumulate(acc, dq_a, True)
+    _accumulate(acc, dq_b, False)
+    return _cast(acc, dq_a)
+
+
+def _dsink_only(q, k, v, out, dout, lse, sink, softmax_scale):
+    # no shard of this rank's own keys is visible: the sink gradient still needs
+    # rowsum(O*dO) and LSE; run the own call on an all-masked single column set
+    idx = torch.zeros((q.shape[0], 1, k.shape[1], 2), dtype=torch.int32, device=q.device)
+    idx[..., 1] = q.shape[1]
+    return _flash_attn_bwd(q, k, v, out, dout, lse, idx, softmax_scale=softmax_scale, causal=False,
+                           learnable_sink=sink, deterministic=True)[3]
 
 
 # ---------------------------------------------------------------------------
@@ -256,16 +295,15 @@ class _CPFunc(torch.autograd.Function):
         ex = TorchDistExchange(group)
         plan = build_plan(local_mask, q.shape[1], False, ex)
         k, v = k.contiguous(), v.contiguous()
-        recv = {o: [torch.empty_like(k), torch.empty_like(v)] for o in plan.pulls()}
+        remote = RemoteKV(k, v, plan.world, plan.rank)
+        recv = {o: remote.recv_buffers(o) for o in plan.pulls()}
         send = {t: [k, v] for t in plan.pushes()}
-        events = ex.exchange(send, recv, plan.pulls())
-        shards = {plan.rank: (k, v)}
-        shards.update({o: tuple(ts) for o, ts in recv.items()})
-        out, lse = cp_forward(q, shards, local_mask, False, softmax_scale, sink, plan, events)
-        ex.finish()
+        ready = ex.exchange(send, recv)                     # overlaps with the own-shard call below
+        masks = _split_mask(local_mask, plan.rank, k.shape[1])
+        out, lse = cp_forward(q, k, v, remote, masks, softmax_scale, sink, plan, ready)
+        torch.cuda.current_stream().wait_stream(ex.comm_stream)
         ctx.save_for_backward(q, k, v, local_mask, out, lse, sink)
-        ctx.shards_remote = {o: ts for o, ts in shards.items() if o != plan.rank}
-        ctx.plan, ctx.ex = plan, ex
+        ctx.remote, ctx.plan, ctx.ex = remote, plan, ex      # pulled shards are kept for the backward
         ctx.softmax_scale, ctx.deterministic = softmax_scale, deterministic
         ctx.mark_non_differentiable(lse)
         return out, lse
@@ -273,55 +311,72 @@ class _CPFunc(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout, dlse):
         q, k, v, local_mask, out, lse, sink = ctx.saved_tensors
-        plan, ex = ctx.plan, ctx.ex
-        shards = {plan.rank: (k, v)}
-        shards.update(ctx.shards_remote)          # pulled shards are kept from the forward
+        plan, ex, remote = ctx.plan, ctx.ex, ctx.remote
         det = ctx.deterministic
         if det is None:
             det = torch.are_deterministic_algorithms_enabled()
-        dq, partials, dsink = cp_backward(q, shards, out, dout.contiguous(), lse, local_mask, False,
-                                          ctx.softmax_scale, sink, det, plan)
-        # partials travel back to the owners; what this rank receives are the
-        # contributions of the ranks that pulled its shard
-        send = {o: list(partials[o]) for o in plan.pulls()}
+        dout = dout.contiguous()
+        own_mask, rest_mask = _split_mask(local_mask, plan.rank, k.shape[1])
+        need_own = plan.need[plan.rank][plan.rank]
+        dq_r = None
+        send, ready = {}, None
         recv = {t: [torch.empty_like(k), torch.empty_like(v)] for t in plan.pushes()}
-        # directions are mirrored with respect to the forward exchange
-        events = _exchange_reverse(ex, send, recv)
-        torch.cuda.current_stream().wait_stream(ex.comm_stream)
-        own = partials.get(plan.rank)
-        by_rank = dict(recv)
+        if plan.pulls():
+            dq_r, dk_all, dv_all = cp_backward_remote(q, remote, out, dout, lse, rest_mask, ctx.softmax_scale, det)
+            send = {o: [remote.slice_of(dk_all, o).contiguous(), remote.slice_of(dv_all, o).contiguous()]
+                    for o in plan.pulls()}
+        if send or recv:
+            ready = ex.exchange_reverse(send, recv)          # overlaps with the own-shard call below
+        dq_o = dsink = None
+        own = None
+        if need_own:
+            dq_o, dk_o, dv_o, dsink = cp_backward_own(q, k, v, out, dout, lse, own_mask, ctx.softmax_scale, sink, det)
+            own = (dk_o, dv_o)
+        elif sink is not None:
+            dsink = _dsink_only(q, k, v, out, dout, lse, sink, ctx.softmax_scale)
+        dq = _sum_dq(dq_o, dq_r)
+        if dq is None:
+            dq = torch.zeros_like(q)
+        if ready is not None:
+            torch.cuda.current_stream().wait_event(ready)
+        by_rank = {t: ts for t, ts in recv.items()}
         if own is not None:
             by_rank[plan.rank] = list(own)
-        ranks = sorted(by_rank)
+        ranks = sorted(by_rank)                              # fixed summation order: by rank
         if ranks:
             dk = _reduce_partials([by_rank[r][0] for r in ranks])
             dv = _reduce_partials([by_rank[r][1] for r in ranks])
         else:
             dk, dv = torch.zeros_like(k), torch.zeros_like(v)
+        torch.cuda.current_stream().wait_stream(ex.comm_stream)
         return dq, dk, dv, None, None, dsink, None, None
 
 
-def _exchange_reverse(ex: TorchDistExchange, send, recv):
-    """Like ``TorchDistExchange.exchange`` with the ring directions swapped:
-    at distance s this rank sends to (rank - s) and receives from (rank + s)."""
-    dist = ex.dist
+def _exchange_reverse(self, send, recv):
+    """Gradient direction: partials go to the shard owners (the ranks this rank
+    pulled from), contributions come from the ranks that pulled this shard."""
+    dist = self.dist
     cur = torch.cuda.current_stream()
-    ex.comm_stream.wait_stream(cur)
-    with torch.cuda.stream(ex.comm_stream):
-        for s in range(1, ex.world):
-            dst, src = (ex.rank - s) % ex.world, (ex.rank + s) % ex.world
-            ops = []
-            if dst in send:
-                ops += [dist.P2POp(dist.isend, t, ex._global(dst), ex.group) for t in send[dst]]
-            if src in recv:
-                ops += [dist.P2POp(dist.irecv, t, ex._global(src), ex.group) for t in recv[src]]
-            if ops:
-                for w in dist.batch_isend_irecv(ops):
-                    w.wait()
+    self.comm_stream.wait_stream(cur)
+    ev = torch.cuda.Event()
+    with torch.cuda.stream(self.comm_stream):
+        ops = []
+        for s in range(1, self.world):
+            for peer, table, fn in (((self.rank - s) % self.world, send, dist.isend),
+                                    ((self.rank + s) % self.world, recv, dist.irecv)):
+                if peer in table:
+                    ops += [dist.P2POp(fn, t, self._global(peer), self.group) for t in table[peer]]
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+        ev.record(self.comm_stream)
     for ts in list(send.values()) + list(recv.values()):
         for t in ts:
-            t.record_stream(ex.comm_stream)
-    return None
+            t.record_stream(self.comm_stream)
+    return ev
+
+
+TorchDistExchange.exchange_reverse = _exchange_reverse
 
 
 def cp_flashmask_attention(query, key, value, startend_row_indices=None, *, causal=False, softmax_scale=None,
@@ -342,32 +397,53 @@ def cp_flashmask_attention(query, key, value, startend_row_indices=None, *, caus
 # ---------------------------------------------------------------------------
 def emulate_cp(qs, ks, vs, douts, local_masks, softmax_scale=None, sink=None, deterministic=True):
     """Run the context-parallel schedule for ``world = len(qs)`` ranks inside
-    one process, in lock-step phases: plans, forward, backward partials, owner
-    reductions.  Returns per-rank lists (out, lse, dq, dk, dv) and dsink."""
+    one process (tests of the arithmetic and of the schedule without several
+    GPUs): plans, forward, backward partials, owner reductions, with exchanges
+    replaced by copies.  Returns per-rank lists (out, lse, dq, dk, dv) and dsink."""
     world = len(qs)
     Sq = qs[0].shape[1]
+    S = ks[0].shape[1]
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(qs[0].shape[-1])
     need = [[bool(x) for x in shard_need_row(local_masks[r], Sq, False, world).cpu().tolist()]
             for r in range(world)]
     plans = [CPPlan(world, r, need) for r in range(world)]
-    shards = {o: (ks[o].contiguous(), vs[o].contiguous()) for o in range(world)}
-    outs, lses, dqs, parts, dsinks = [], [], [], [], []
+    ks = [k.contiguous() for k in ks]
+    vs = [v.contiguous() for v in vs]
+    remotes, outs, lses = [], [], []
     for r in range(world):
-        mine = {o: shards[o] for o in [r] + plans[r].pulls()}
-        out, lse = cp_forward(qs[r], mine, local_masks[r], False, softmax_scale, sink, plans[r])
+        rem = RemoteKV(ks[r], vs[r], world, r)
+        for o in plans[r].pulls():
+            bufs = rem.recv_buffers(o)
+            bufs[0].copy_(ks[o]); bufs[1].copy_(vs[o])
+        remotes.append(rem)
+        out, lse = cp_forward(qs[r], ks[r], vs[r], rem, _split_mask(local_masks[r], r, S), softmax_scale, sink,
+                              plans[r])
         outs.append(out); lses.append(lse)
+    dqs, contrib, dsinks = [], {o: {} for o in range(world)}, []
     for r in range(world):
-        mine = {o: shards[o] for o in [r] + plans[r].pulls()}
-        dq, p_r, ds = cp_backward(qs[r], mine, outs[r], douts[r], lses[r], local_masks[r], False, softmax_scale,
-                                  sink, deterministic, plans[r])
-        dqs.append(dq); parts.append(p_r); dsinks.append(ds)
+        own_mask, rest_mask = _split_mask(local_masks[r], r, S)
+        dq_r = dq_o = ds = None
+        if plans[r].pulls():
+            dq_r, dk_all, dv_all = cp_backward_remote(qs[r], remotes[r], outs[r], douts[r], lses[r], rest_mask,
+                                                      softmax_scale, deterministic)
+            for o in plans[r].pulls():
+                contrib[o][r] = (remotes[r].slice_of(dk_all, o), remotes[r].slice_of(dv_all, o))
+        if need[r][r]:
+            dq_o, dk_o, dv_o, ds = cp_backward_own(qs[r], ks[r], vs[r], outs[r], douts[r], lses[r], own_mask,
+                                                   softmax_scale, sink, deterministic)
+            contrib[r][r] = (dk_o, dv_o)
+        elif sink is not None:
+            ds = _dsink_only(qs[r], ks[r], vs[r], outs[r], douts[r], lses[r], sink, softmax_scale)
+        dq = _sum_dq(dq_o, dq_r)
+        dqs.append(dq if dq is not None else torch.zeros_like(qs[r]))
+        dsinks.append(ds)
     dks, dvs = [], []
     for o in range(world):
-        contrib = [parts[r][o] for r in range(world) if o in parts[r]]
-        if contrib:
-            dks.append(_reduce_partials([c[0] for c in contrib]))
-            dvs.append(_reduce_partials([c[1] for c in contrib]))
+        ranks = sorted(contrib[o])
+        if ranks:
+            dks.append(_reduce_partials([contrib[o][r][0] for r in ranks]))
+            dvs.append(_reduce_partials([contrib[o][r][1] for r in ranks]))
         else:
             dks.append(torch.zeros_like(ks[o])); dvs.append(torch.zeros_like(vs[o]))
     dsink = None

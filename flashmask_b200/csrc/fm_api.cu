@@ -37,6 +37,7 @@ size_t bwd_sm100_workspace_bytes(const fm_attn_args* a);
 
 int fwd_sm100_status(int* out, bool reset);
 int bwd_sm100_status(int* out, bool reset);
+int bounded_wait_selftest_launch(uint64_t budget_ns, cudaStream_t s);
 
 static inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
@@ -211,6 +212,12 @@ extern "C" int fm_kernel_status(int* status, int reset) {
   rc = bwd_sm100_status(&bw, reset != 0);
   *status = f ? f : bw;
   return rc;
+}
+
+extern "C" int fm_selftest_bounded_wait(int budget_us, void* stream) {
+  FM_REQUIRE(budget_us > 0 && budget_us <= 1000000, FM_ERR_INVALID_ARGUMENT,
+             "fm_selftest_bounded_wait: budget must be in (0, 1 s]");
+  return bounded_wait_selftest_launch((uint64_t)budget_us * 1000ull, (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------

@@ -93,22 +93,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
   const int n_heads = (MODE == MODE_DKDV) ? G : 1;
 
   if (tid == 0) misc[4] = 0;
-  if (warp == 8 && lane == 0) {
-    mbar_init(bar(Cfg::B_STAT), 1);
-    for (int i = 0; i < Cfg::NSLOT; ++i) {
-      mbar_init(bar(Cfg::B_RFULL + i), MODE == MODE_DQ ? 33 : 1);
-      mbar_init(bar(Cfg::B_REMPTY + i), 1);
-    }
-    for (int h = 0; h < 2; ++h) { mbar_init(bar(Cfg::B_GFULL + h), 1); mbar_init(bar(Cfg::B_TFULL + h), 128); }
-    mbar_init(bar(Cfg::B_ACC), 1);
-    fence_mbar_init();
-    tma_prefetch_desc(&tm_stat1); tma_prefetch_desc(&tm_stat2);
-    tma_prefetch_desc(&tm_str1); tma_prefetch_desc(&tm_str2);
-  }
-  if (warp == 9) {
-    tmem_alloc(sbase + Cfg::OFF_MISC, 512);
-    tmem_relinquish();
-  }
   if (warp == 10) {
     int cnt = 0;
     if (MODE == MODE_DKDV) {
@@ -147,11 +131,50 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
     }
     if (lane == 0) misc[1] = min(cnt, Cfg::LIST_MAX);
   }
+  __syncthreads();
+  const int cnt = misc[1];
+  if (cnt == 0) {
+    // this tile's gradients are all zero: store them and leave before touching
+    // barriers or TMEM
+    if (MODE == MODE_DKDV) {
+      uint16_t* gk = reinterpret_cast<uint16_t*>(p.dk) + b * p.dk_b + (int64_t)row0 * p.dk_s + hk * p.dk_h;
+      uint16_t* gv = reinterpret_cast<uint16_t*>(p.dv) + b * p.dv_b + (int64_t)row0 * p.dv_s + hk * p.dv_h;
+      for (int x = tid; x < 128 * 16; x += Cfg::NTHREADS) {
+        const int rr = x >> 4, cc = x & 15;
+        if (row0 + rr < p.Sk) {
+          *reinterpret_cast<uint4*>(gk + (int64_t)rr * p.dk_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(gv + (int64_t)rr * p.dv_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+    } else {
+      uint16_t* gq = reinterpret_cast<uint16_t*>(p.dq) + b * p.dq_b + (int64_t)row0 * p.dq_s + hq0 * p.dq_h;
+      for (int x = tid; x < 128 * 16; x += Cfg::NTHREADS) {
+        const int rr = x >> 4, cc = x & 15;
+        if (row0 + rr < p.Sq) *reinterpret_cast<uint4*>(gq + (int64_t)rr * p.dq_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    return;
+  }
+  if (warp == 8 && lane == 0) {
+    mbar_init(bar(Cfg::B_STAT), 1);
+    for (int i = 0; i < Cfg::NSLOT; ++i) {
+      mbar_init(bar(Cfg::B_RFULL + i), MODE == MODE_DQ ? 33 : 1);
+      mbar_init(bar(Cfg::B_REMPTY + i), 1);
+    }
+    for (int h = 0; h < 2; ++h) { mbar_init(bar(Cfg::B_GFULL + h), 1); mbar_init(bar(Cfg::B_TFULL + h), 128); }
+    mbar_init(bar(Cfg::B_ACC), 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_stat1); tma_prefetch_desc(&tm_stat2);
+    tma_prefetch_desc(&tm_str1); tma_prefetch_desc(&tm_str2);
+  }
+  if (warp == 9) {
+    tmem_alloc(sbase + Cfg::OFF_MISC, 512);
+    tmem_relinquish();
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = (uint32_t)misc[0];
-  const int cnt = misc[1];
   const int K_items = cnt * n_heads;
   WaitCtx wc{misc + 4, global_timer_ns() + 2000000000ull};
   // TMEM columns: G1_p at 64p, G2_p at 128+64p, accumulators at 256 (dV | dQ) and 384 (dK)

@@ -80,20 +80,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int off = p.Sk - p.Sq;
 
   if (tid == 0) misc[4] = 0;
-  if (warp == 8 && lane == 0) {
-    mbar_init(bar(Cfg::B_QFULL + 0), 1); mbar_init(bar(Cfg::B_QFULL + 1), 1);
-    for (int i = 0; i < Cfg::NSTAGE; ++i) { mbar_init(bar(Cfg::B_KVFULL + i), 1); mbar_init(bar(Cfg::B_KVEMPTY + i), 1); }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(bar(Cfg::B_SFULL + s), 1); mbar_init(bar(Cfg::B_PFULL + s), 128); mbar_init(bar(Cfg::B_ODONE + s), 1);
-    }
-    for (int i = 0; i < Cfg::NBND; ++i) { mbar_init(bar(Cfg::B_BNDFULL + i), 32); mbar_init(bar(Cfg::B_BNDEMPTY + i), 256); }
-    fence_mbar_init();
-    tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
-  }
-  if (warp == 9) {
-    tmem_alloc(sbase + Cfg::OFF_MISC, 512);
-    tmem_relinquish();
-  }
   if (warp == 10) {
     // surviving K tiles, right to left, with the flags of both sub-tiles
     const int nb = (p.Sk + 127) / 128;
@@ -118,11 +104,39 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
     if (lane == 0) { misc[1] = min(cnt, Cfg::LIST_MAX); misc[2] = c0; misc[3] = c1; }
   }
+  __syncthreads();
+  const int cnt = misc[1];
+  if (cnt == 0) {
+    // nothing visible for these 256 rows: write O = 0 and LSE = -inf (sink
+    // present: LSE = sink) and leave before touching barriers or TMEM
+    uint16_t* go = reinterpret_cast<uint16_t*>(p.o) + b * p.o_b + (int64_t)ms * p.o_s + hq * p.o_h;
+    for (int x = tid; x < 256 * (DV / 8); x += Cfg::NTHREADS) {
+      const int rr = x / (DV / 8), cc = x % (DV / 8);
+      if (ms + rr < p.Sq) *reinterpret_cast<uint4*>(go + (int64_t)rr * p.o_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    const float empty_lse = p.sink ? p.sink[hq] : neg_inf();
+    for (int rr = tid; rr < 256; rr += Cfg::NTHREADS)
+      if (ms + rr < p.Sq) p.lse[((int64_t)b * p.Hq + hq) * p.Sq + ms + rr] = empty_lse;
+    return;
+  }
+  if (warp == 8 && lane == 0) {
+    mbar_init(bar(Cfg::B_QFULL + 0), 1); mbar_init(bar(Cfg::B_QFULL + 1), 1);
+    for (int i = 0; i < Cfg::NSTAGE; ++i) { mbar_init(bar(Cfg::B_KVFULL + i), 1); mbar_init(bar(Cfg::B_KVEMPTY + i), 1); }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(Cfg::B_SFULL + s), 1); mbar_init(bar(Cfg::B_PFULL + s), 128); mbar_init(bar(Cfg::B_ODONE + s), 1);
+    }
+    for (int i = 0; i < Cfg::NBND; ++i) { mbar_init(bar(Cfg::B_BNDFULL + i), 32); mbar_init(bar(Cfg::B_BNDEMPTY + i), 256); }
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 9) {
+    tmem_alloc(sbase + Cfg::OFF_MISC, 512);
+    tmem_relinquish();
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = (uint32_t)misc[0];
-  const int cnt = misc[1];
   const int cnt_s[2] = {misc[2], misc[3]};
   WaitCtx wc{misc + 4, global_timer_ns() + 2000000000ull};
 
@@ -460,6 +474,30 @@ int make_bshd_tmap(CUtensorMap* out, const void* base, int dtype, int B, int S, 
 }
 
 }  // namespace sm100
+
+// One CTA waits on an mbarrier that nothing ever arrives on, with a wall-clock
+// budget: exercises the bounded wait and the status word without touching the
+// tensor pipe.  The kernel returns normally; the context stays usable.
+__global__ void bounded_wait_selftest_kernel(uint64_t budget_ns) {
+  __shared__ __align__(8) uint64_t never;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&never), 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  WaitCtx wc{&abort_flag, global_timer_ns() + budget_ns};
+  const bool ok = mbar_wait(smem_u32(&never), 0u, wc);
+  __syncthreads();
+  if (threadIdx.x == 0 && !ok) atomicExch(&g_fwd_status, FM_ERR_TIMEOUT);
+}
+
+int bounded_wait_selftest_launch(uint64_t budget_ns, cudaStream_t s) {
+  bounded_wait_selftest_kernel<<<1, 64, 0, s>>>(budget_ns);
+  FM_CUDA_TRY(cudaGetLastError());
+  return FM_OK;
+}
 
 bool fwd_sm100_supported(const fm_attn_args* a) {
   if (!(a->d == 128 && a->dv == 128)) return false;

@@ -140,6 +140,12 @@ def _check_shapes(q, k, v, idx, causal):
             assert idx.shape[-1] in (2, 4), "non-causal masks carry 2 or 4 bounds per column"
 
 
+def _kv_shared(k: torch.Tensor, v: torch.Tensor) -> bool:
+    """True when ``v`` is ``k[..., :dv]`` on the same storage (MLA-style shared K/V)."""
+    return (v.data_ptr() == k.data_ptr() and v.shape[-1] <= k.shape[-1] and v.shape[:-1] == k.shape[:-1]
+            and v.stride() == k.stride())
+
+
 def _sink_fp32(sink, Hq, device):
     if sink is None:
         return None
@@ -210,6 +216,13 @@ def _flash_attn_bwd(q, k, v, out, dout, lse, startend_row_indices=None, softmax_
     ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=q.device)
     a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
     _lib.check(lib.fm_bwd(C.byref(a), _stream(q)), "fm_bwd")
+    if _kv_shared(k, v):
+        # value is a view of key's leading dv columns on the same storage: the
+        # gradient of that storage is dK with dV folded into its leading columns,
+        # and the value slot returns zeros (reference convention,
+        # flashmask/cute/ops/_common.py:52-88)
+        dk[..., :dv] += dvv
+        dvv.zero_()
     dsink = None
     if dsink32 is not None:
         dsink = dsink32.to(learnable_sink.dtype).reshape(learnable_sink.shape)

@@ -159,6 +159,14 @@ FM_API int fm_fwd(const fm_attn_args* args, void* stream);
  * (flashmask/cute/barrier.py:95-148). */
 FM_API int fm_kernel_status(int* status, int reset);
 
+/* Launches one CTA that waits, with a budget of `budget_us` microseconds, on a
+ * barrier nothing arrives on: the wait gives up, the kernel returns normally
+ * and fm_kernel_status reports FM_ERR_TIMEOUT.  Failure-detection self test of
+ * the bounded-wait machinery every tcgen05 kernel uses; no GPU fault, trap or
+ * hang is involved.  (The reference's watchdog traps instead,
+ * flashmask/cute/barrier.py:95-148.) */
+FM_API int fm_selftest_bounded_wait(int budget_us, void* stream);
+
 /* Backward: dQ, dK, dV (and dsink when sink != NULL).
  * Replaces _flash_attn_bwd (flashmask/cute/ops/bwd.py:56-1261): preprocess
  * (flash_bwd_preprocess.py:184-342), main (flash_bwd_sm100.py:1435-),

@@ -224,3 +224,38 @@ def test_errors():
         fm.flashmask_attention(q.cuda()[..., :40].contiguous().repeat(1, 1, 1, 8),
                                k.cuda()[..., :40].contiguous().repeat(1, 1, 1, 8),
                                v.cuda()[..., :40].contiguous().repeat(1, 1, 1, 8))
+
+
+def test_bounded_wait_reports_timeout_without_fault():
+    """A wait on a barrier nothing arrives on gives up after its budget, the kernel
+    returns, the status word says FM_ERR_TIMEOUT and the context keeps working."""
+    from flashmask_b200 import _lib
+    assert _kernel_status() == 0
+    _lib.check(_lib.load().fm_selftest_bounded_wait(2000, torch.cuda.current_stream().cuda_stream),
+               "fm_selftest_bounded_wait")
+    torch.cuda.synchronize()
+    assert _kernel_status() == 5          # FM_ERR_TIMEOUT, and the read cleared it
+    assert _kernel_status() == 0
+    x = torch.ones(8, device="cuda")
+    assert float(x.sum()) == 8.0          # the context is still usable
+    _run("causal_doc", 1, 256, 256, 2, 2, 128, 128, seed=2)
+
+
+def test_shared_kv_convention():
+    """value = key[..., :dv] on the same storage (576/512): dv comes back zero and dk
+    carries dK + dV (reference: flashmask/cute/ops/_common.py:52-88)."""
+    B, S, Hq, Hkv, d, dv = 1, 256, 2, 1, 576, 512
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(B, S, Hq, d, generator=g).bfloat16().cuda()
+    kv = torch.randn(B, S, Hkv, d, generator=g).bfloat16().cuda()
+    do = torch.randn(B, S, Hq, dv, generator=g).bfloat16().cuda()
+    k, v = kv, kv[..., :dv]
+    out, lse = fm._flash_attn_fwd(q, k, v, None, causal=True)
+    dq, dk, dvv, _ = fm._flash_attn_bwd(q, k, v, out, do, lse, None, causal=True)
+    assert float(dvv.abs().max()) == 0.0
+    v2 = v.contiguous()                    # separate storage: plain gradients
+    dq2, dk2, dv2, _ = fm._flash_attn_bwd(q, k, v2, out, do, lse, None, causal=True)
+    want = dk2.float()
+    want[..., :dv] += dv2.float()
+    assert torch.equal(dq, dq2)
+    assert (dk.float() - want).abs().max().item() <= 2 ** -6 * max(1.0, want.abs().max().item())
