@@ -447,25 +447,31 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
         constexpr uint32_t idesc_g = make_idesc(IS_BF16, 128, 64, 0, 0);
         constexpr uint32_t idesc_acc = make_idesc(IS_BF16, 128, 128, 0, 1);
         bool ok = mbar_wait(bar(Cfg::B_STAT), 0u, wc);
+        // descriptors are built once; per MMA only a constant is added to the
+        // 14-bit address field (all smem offsets are multiples of 16 bytes)
+        const uint64_t dA1 = make_sdesc(sStat, 16, 1024);
+        const uint64_t dA2 = make_sdesc(sStat + Cfg::TILE_BYTES, 16, 1024);
+        const uint64_t dRk = make_sdesc(sRing, 16, 1024);            // K-major view of a ring slot
+        const uint64_t dRm = make_sdesc(sRing, Cfg::SUB64, 1024);    // MN-major view of a ring slot
         auto issue_g = [&](int k) {
           const int slot = k % Cfg::NSLOT, pz = k & 1;
           ok = ok && mbar_wait(bar(Cfg::B_RFULL + slot), (uint32_t)(k / Cfg::NSLOT) & 1u, wc);
           if (!ok) return;
           tc_fence_after();
-          const uint32_t bsl = sRing + slot * Cfg::SLOT_BYTES;
+          const uint64_t db1 = dRk + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));
+          const uint64_t db2 = db1 + (uint64_t)(Cfg::HALF_BYTES >> 4);
+          const uint32_t g1 = tmem + C_G1 + 64u * pz, g2 = tmem + C_G2 + 64u * pz;
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
-            const uint32_t oa = (uint32_t)(kk >> 2) * Cfg::SUB128 + (uint32_t)(kk & 3) * 32u;
-            const uint32_t ob = (uint32_t)(kk >> 2) * Cfg::SUB64 + (uint32_t)(kk & 3) * 32u;
-            umma_ss(tmem + C_G1 + 64u * pz, make_sdesc(sStat + oa, 16, 1024), make_sdesc(bsl + ob, 16, 1024),
-                    idesc_g, kk > 0 ? 1u : 0u);
+            const uint64_t oa = (uint64_t)(((kk >> 2) * Cfg::SUB128 + (kk & 3) * 32) >> 4);
+            const uint64_t ob = (uint64_t)(((kk >> 2) * Cfg::SUB64 + (kk & 3) * 32) >> 4);
+            umma_ss(g1, dA1 + oa, db1 + ob, idesc_g, kk > 0 ? 1u : 0u);
           }
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
-            const uint32_t oa = (uint32_t)(kk >> 2) * Cfg::SUB128 + (uint32_t)(kk & 3) * 32u;
-            const uint32_t ob = (uint32_t)(kk >> 2) * Cfg::SUB64 + (uint32_t)(kk & 3) * 32u;
-            umma_ss(tmem + C_G2 + 64u * pz, make_sdesc(sStat + Cfg::TILE_BYTES + oa, 16, 1024),
-                    make_sdesc(bsl + Cfg::HALF_BYTES + ob, 16, 1024), idesc_g, kk > 0 ? 1u : 0u);
+            const uint64_t oa = (uint64_t)(((kk >> 2) * Cfg::SUB128 + (kk & 3) * 32) >> 4);
+            const uint64_t ob = (uint64_t)(((kk >> 2) * Cfg::SUB64 + (kk & 3) * 32) >> 4);
+            umma_ss(g2, dA2 + oa, db2 + ob, idesc_g, kk > 0 ? 1u : 0u);
           }
           tc_commit(bar(Cfg::B_GFULL + pz));
         };
@@ -476,21 +482,20 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
           ok = mbar_wait(bar(Cfg::B_TFULL + pz), (uint32_t)(k >> 1) & 1u, wc);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t bsl = sRing + slot * Cfg::SLOT_BYTES;
+          const uint64_t dm1 = dRm + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));     // streamed operand 1
+          const uint64_t dm2 = dm1 + (uint64_t)(Cfg::HALF_BYTES >> 4);               // streamed operand 2
           const uint32_t acc_on = k > 0 ? 1u : 0u;
+          const uint32_t t1 = tmem + C_G1 + 64u * pz + 32u, t2 = tmem + C_G2 + 64u * pz + 32u;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t ok16 = (uint64_t)(kk * (2048 >> 4));
             if (MODE == MODE_DKDV) {
               // dV += P^T dO (streamed operand 2), dK += dS^T Q (streamed operand 1)
-              umma_ts(tmem + C_ACC1, tmem + C_G1 + 64u * pz + 32u + 8u * kk,
-                      make_sdesc(bsl + Cfg::HALF_BYTES + kk * 2048u, Cfg::SUB64, 1024), idesc_acc,
-                      (acc_on || kk > 0) ? 1u : 0u);
-              umma_ts(tmem + C_ACC2, tmem + C_G2 + 64u * pz + 32u + 8u * kk,
-                      make_sdesc(bsl + kk * 2048u, Cfg::SUB64, 1024), idesc_acc, (acc_on || kk > 0) ? 1u : 0u);
+              umma_ts(tmem + C_ACC1, t1 + 8u * kk, dm2 + ok16, idesc_acc, kk > 0 ? 1u : acc_on);
+              umma_ts(tmem + C_ACC2, t2 + 8u * kk, dm1 + ok16, idesc_acc, kk > 0 ? 1u : acc_on);
             } else {
               // dQ += dS K (streamed operand 1)
-              umma_ts(tmem + C_ACC1, tmem + C_G2 + 64u * pz + 32u + 8u * kk,
-                      make_sdesc(bsl + kk * 2048u, Cfg::SUB64, 1024), idesc_acc, (acc_on || kk > 0) ? 1u : 0u);
+              umma_ts(tmem + C_ACC1, t2 + 8u * kk, dm1 + ok16, idesc_acc, kk > 0 ? 1u : acc_on);
             }
           }
           tc_commit(bar(Cfg::B_REMPTY + slot));

@@ -372,18 +372,24 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         int npv[2] = {0, 0};
         bool q_ready[2] = {false, false};
         bool ok = true;
+        // descriptors are built once; per MMA only a constant is added to the
+        // 14-bit address field (all smem offsets are multiples of 16 bytes)
+        const uint64_t dq0 = make_sdesc(sQ, 16, 1024);
+        const uint64_t dk0 = make_sdesc(sKV, 16, 1024);
+        const uint64_t dv0 = make_sdesc(sKV, Cfg::SUB, 1024);
         auto issue_qk = [&](int s, int i) {
           const int k = 2 * i, slot = k % Cfg::NSTAGE;
           ok = ok && mbar_wait(bar(Cfg::B_KVFULL + slot), (uint32_t)(k / Cfg::NSTAGE) & 1u, wc);
           if (ok && !q_ready[s]) { ok = mbar_wait(bar(Cfg::B_QFULL + s), 0u, wc); q_ready[s] = true; }
           if (!ok) return;
           tc_fence_after();
-          const uint32_t a0 = sQ + s * Cfg::Q_BYTES, b0 = sKV + slot * Cfg::SLOT_BYTES;
+          const uint64_t da = dq0 + (uint64_t)(s * (Cfg::Q_BYTES >> 4));
+          const uint64_t db = dk0 + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));
+          const uint32_t dst = tmem + 128u * s;
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t o = (uint32_t)(kk >> 2) * Cfg::SUB + (uint32_t)(kk & 3) * 32u;
-            umma_ss(tmem + 128u * s, make_sdesc(a0 + o, 16, 1024), make_sdesc(b0 + o, 16, 1024), idesc_qk,
-                    kk > 0 ? 1u : 0u);
+            const uint64_t o = (uint64_t)(((kk >> 2) * Cfg::SUB + (kk & 3) * 32) >> 4);
+            umma_ss(dst, da + o, db + o, idesc_qk, kk > 0 ? 1u : 0u);
           }
           tc_commit(bar(Cfg::B_SFULL + s));
         };
@@ -393,11 +399,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ok = ok && mbar_wait(bar(Cfg::B_PFULL + s), (uint32_t)npv[s] & 1u, wc);
           if (!ok) return;
           tc_fence_after();
-          const uint32_t v0 = sKV + slot * Cfg::SLOT_BYTES;
+          const uint64_t db = dv0 + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));
+          const uint32_t dst = tmem + 256u + 128u * s, src = tmem + 128u * s + 64u;
+          const uint32_t acc0 = npv[s] > 0 ? 1u : 0u;
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            umma_ts(tmem + 256u + 128u * s, tmem + 128u * s + 64u + 8u * kk,
-                    make_sdesc(v0 + kk * 2048u, Cfg::SUB, 1024), idesc_pv, (npv[s] > 0 || kk > 0) ? 1u : 0u);
+            umma_ts(dst, src + 8u * kk, db + (uint64_t)(kk * (2048 >> 4)), idesc_pv, kk > 0 ? 1u : acc0);
           tc_commit(bar(Cfg::B_ODONE + s));
           ++npv[s];
         };
