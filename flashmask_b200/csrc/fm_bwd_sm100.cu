@@ -161,7 +161,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
       mbar_init(bar(Cfg::B_RFULL + i), MODE == MODE_DQ ? 33 : 1);
       mbar_init(bar(Cfg::B_REMPTY + i), 1);
     }
-    for (int h = 0; h < 2; ++h) { mbar_init(bar(Cfg::B_GFULL + h), 1); mbar_init(bar(Cfg::B_TFULL + h), 128); }
+    for (int h = 0; h < 2; ++h) { mbar_init(bar(Cfg::B_GFULL + h), 1); mbar_init(bar(Cfg::B_TFULL + h), 4); }
     mbar_init(bar(Cfg::B_ACC), 1);
     fence_mbar_init();
     tma_prefetch_desc(&tm_stat1); tma_prefetch_desc(&tm_stat2);
@@ -182,7 +182,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
 
   if (warp < 8) {
     // =========================== compute warpgroups ===========================
-    setmaxnreg_inc<200>();
     const int pz = warp >> 2;                    // item parity this warpgroup serves
     const int r = tid & 127;                     // TMEM lane
     const uint32_t lane_field = (uint32_t)((warp & 3) * 32) << 16;
@@ -219,95 +218,103 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
       ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_GFULL + pz), (uint32_t)(k >> 1) & 1u, wc));
       if (!ok) break;
       tc_fence_after();
-      uint32_t sr[64], dr[64];
-      tmem_ld32(tG1, sr); tmem_ld32(tG1 + 32, sr + 32);
-      tmem_ld32(tG2, dr); tmem_ld32(tG2 + 32, dr + 32);
-      tc_wait_ld();
       const uint8_t* aux = smem + Cfg::OFF_AUX + slot * Cfg::AUX_BYTES;
       const uint32_t NEG = 0xff800000u;
-      uint32_t pk1[32], pk2[32];
-      if (MODE == MODE_DKDV) {
-        // columns are queries i0 + c; this lane is key j
-        const int i0 = idx * 64;
-        if (flags & ~FM_TF_ACTIVE) {
-          const int a0 = lts - i0, a1 = lte - i0, b0 = uts - i0, b1 = ute - i0;
-          const int cz = md.causal ? (row0 + r - off - i0) : INT_MIN;   // masked while c < cz
+      // 64 score columns in two chunks of 32: the second chunk is in flight while
+      // the first is processed; the bf16 results overlay the LOWER half of the
+      // score buffers (columns already consumed by then)
+      uint32_t sr[2][32], dr[2][32];
+      tmem_ld32(tG1, sr[0]); tmem_ld32(tG2, dr[0]);
+      tc_wait_ld();
+      tmem_ld32(tG1 + 32, sr[1]); tmem_ld32(tG2 + 32, dr[1]);
 #pragma unroll
-          for (int c = 0; c < 64; ++c)
-            if ((c >= a0 && c < a1) || (c >= b0 && c < b1) || c < cz) sr[c] = NEG;
-        }
-        const float4* st = reinterpret_cast<const float4*>(aux);
+      for (int hc = 0; hc < 2; ++hc) {
+        if (hc == 1) tc_wait_ld();
+        uint32_t pk1[16], pk2[16];
+        if (MODE == MODE_DKDV) {
+          // columns are queries i0 + c; this lane is key j
+          const int i0 = idx * 64 + 32 * hc;
+          if (flags & ~FM_TF_ACTIVE) {
+            const int a0 = lts - i0, a1 = lte - i0, b0 = uts - i0, b1 = ute - i0;
+            const int cz = md.causal ? (row0 + r - off - i0) : INT_MIN;   // masked while c < cz
 #pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4) {
-          const float4 l4 = st[c4], d4 = st[16 + c4];
-          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv4[4] = {d4.x, d4.y, d4.z, d4.w};
-          float pe[4], de[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            pe[u] = fast_exp2(fmaf(__uint_as_float(sr[4 * c4 + u]), scale_log2, -lv[u]));
-            de[u] = pe[u] * (__uint_as_float(dr[4 * c4 + u]) - dv4[u]);
+            for (int c = 0; c < 32; ++c)
+              if ((c >= a0 && c < a1) || (c >= b0 && c < b1) || c < cz) sr[hc][c] = NEG;
           }
-          pk1[2 * c4] = pack2<IS_BF16>(pe[0], pe[1]); pk1[2 * c4 + 1] = pack2<IS_BF16>(pe[2], pe[3]);
-          pk2[2 * c4] = pack2<IS_BF16>(de[0], de[1]); pk2[2 * c4 + 1] = pack2<IS_BF16>(de[2], de[3]);
-        }
-        tmem_st32(tG1 + 32, pk1);
-        tmem_st32(tG2 + 32, pk2);
-      } else {
-        // columns are keys jh0 + c; this lane is query i
-        const int jh0 = idx * 64;
-        const int i = row0 + r;
-        if (flags & FM_TF_BOUNDS) {
-          const int4* bp = reinterpret_cast<const int4*>(aux);
-          if (md.ncols == 1) {
+          const float4* st = reinterpret_cast<const float4*>(aux) + 8 * hc;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int4 v = bp[j];
-              if (i >= v.x) sr[4 * j] = NEG;
-              if (i >= v.y) sr[4 * j + 1] = NEG;
-              if (i >= v.z) sr[4 * j + 2] = NEG;
-              if (i >= v.w) sr[4 * j + 3] = NEG;
+          for (int c4 = 0; c4 < 8; ++c4) {
+            const float4 l4 = st[c4], d4 = st[16 + c4];
+            const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv4[4] = {d4.x, d4.y, d4.z, d4.w};
+            float pe[4], de[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              pe[u] = fast_exp2(fmaf(__uint_as_float(sr[hc][4 * c4 + u]), scale_log2, -lv[u]));
+              de[u] = pe[u] * (__uint_as_float(dr[hc][4 * c4 + u]) - dv4[u]);
             }
-          } else if (md.ncols == 2 && md.causal) {
+            pk1[2 * c4] = pack2<IS_BF16>(pe[0], pe[1]); pk1[2 * c4 + 1] = pack2<IS_BF16>(pe[2], pe[3]);
+            pk2[2 * c4] = pack2<IS_BF16>(de[0], de[1]); pk2[2 * c4 + 1] = pack2<IS_BF16>(de[2], de[3]);
+          }
+          tmem_st16(tG1 + 16 * hc, pk1);
+          tmem_st16(tG2 + 16 * hc, pk2);
+        } else {
+          // columns are keys jh0 + c; this lane is query i
+          const int jh0 = idx * 64 + 32 * hc;
+          const int i = row0 + r;
+          if (flags & FM_TF_BOUNDS) {
+            const int4* bp = reinterpret_cast<const int4*>(aux) + (8 * md.ncols) * hc;
+            if (md.ncols == 1) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int4 v = bp[j];
-              if (i >= v.x && i < v.y) sr[2 * j] = NEG;
-              if (i >= v.z && i < v.w) sr[2 * j + 1] = NEG;
-            }
-          } else if (md.ncols == 2) {
+              for (int j = 0; j < 8; ++j) {
+                const int4 v = bp[j];
+                if (i >= v.x) sr[hc][4 * j] = NEG;
+                if (i >= v.y) sr[hc][4 * j + 1] = NEG;
+                if (i >= v.z) sr[hc][4 * j + 2] = NEG;
+                if (i >= v.w) sr[hc][4 * j + 3] = NEG;
+              }
+            } else if (md.ncols == 2 && md.causal) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int4 v = bp[j];
-              if (i >= v.x || i < v.y) sr[2 * j] = NEG;
-              if (i >= v.z || i < v.w) sr[2 * j + 1] = NEG;
-            }
-          } else {
+              for (int j = 0; j < 16; ++j) {
+                const int4 v = bp[j];
+                if (i >= v.x && i < v.y) sr[hc][2 * j] = NEG;
+                if (i >= v.z && i < v.w) sr[hc][2 * j + 1] = NEG;
+              }
+            } else if (md.ncols == 2) {
 #pragma unroll
-            for (int j = 0; j < 64; ++j) {
-              const int4 v = bp[j];
-              if ((i >= v.x && i < v.y) || (i >= v.z && i < v.w)) sr[j] = NEG;
+              for (int j = 0; j < 16; ++j) {
+                const int4 v = bp[j];
+                if (i >= v.x || i < v.y) sr[hc][2 * j] = NEG;
+                if (i >= v.z || i < v.w) sr[hc][2 * j + 1] = NEG;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int4 v = bp[j];
+                if ((i >= v.x && i < v.y) || (i >= v.z && i < v.w)) sr[hc][j] = NEG;
+              }
             }
           }
-        }
-        if (flags & (FM_TF_CAUSAL | FM_TF_RAGGED)) {
-          int jmax = p.Sk - 1 - jh0;
-          if (md.causal) jmax = min(jmax, i + off - jh0);
+          if (flags & (FM_TF_CAUSAL | FM_TF_RAGGED)) {
+            int jmax = p.Sk - 1 - jh0;
+            if (md.causal) jmax = min(jmax, i + off - jh0);
 #pragma unroll
-          for (int c = 0; c < 64; ++c)
-            if (c > jmax) sr[c] = NEG;
-        }
+            for (int c = 0; c < 32; ++c)
+              if (c > jmax) sr[hc][c] = NEG;
+          }
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), scale_log2, -lse2_row));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), scale_log2, -lse2_row));
-          pk2[c] = pack2<IS_BF16>(p0 * (__uint_as_float(dr[2 * c]) - dps_row),
-                                  p1 * (__uint_as_float(dr[2 * c + 1]) - dps_row));
+          for (int c = 0; c < 16; ++c) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[hc][2 * c]), scale_log2, -lse2_row));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[hc][2 * c + 1]), scale_log2, -lse2_row));
+            pk2[c] = pack2<IS_BF16>(p0 * (__uint_as_float(dr[hc][2 * c]) - dps_row),
+                                    p1 * (__uint_as_float(dr[hc][2 * c + 1]) - dps_row));
+          }
+          tmem_st16(tG2 + 16 * hc, pk2);
         }
-        tmem_st32(tG2 + 32, pk2);
       }
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(Cfg::B_TFULL + pz));
+      __syncwarp();
+      if (lane == 0)       mbar_arrive(bar(Cfg::B_TFULL + pz));
     }
 
     // ---- epilogue ----
@@ -389,7 +396,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
       }
     }
   } else {
-    setmaxnreg_dec<64>();
     if (warp == 8) {
       // =========================== producer ===========================
       if (lane == 0 && K_items > 0) {
@@ -485,7 +491,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
           const uint64_t dm1 = dRm + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));     // streamed operand 1
           const uint64_t dm2 = dm1 + (uint64_t)(Cfg::HALF_BYTES >> 4);               // streamed operand 2
           const uint32_t acc_on = k > 0 ? 1u : 0u;
-          const uint32_t t1 = tmem + C_G1 + 64u * pz + 32u, t2 = tmem + C_G2 + 64u * pz + 32u;
+          const uint32_t t1 = tmem + C_G1 + 64u * pz, t2 = tmem + C_G2 + 64u * pz;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             const uint64_t ok16 = (uint64_t)(kk * (2048 >> 4));
