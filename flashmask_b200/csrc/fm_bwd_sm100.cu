@@ -30,6 +30,24 @@ __device__ int g_bwd_status = 0;
 
 constexpr int MODE_DKDV = 0, MODE_DQ = 1;
 
+#ifdef FM_TRACE
+// Debug build only: timeline of CTA (0,0,0); every tracing thread appends
+// (event, item, SM clock) triples to its own lane of the buffer with plain stores.
+__device__ int g_trace[4 * 3 * 2048];
+__device__ __forceinline__ void trace_ev(int role, int& n, int ev, int k) {
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && n < 2048) {
+    int* t = g_trace + (role * 2048 + n) * 3;
+    t[0] = ev; t[1] = k; t[2] = (int)clock64();
+    ++n;
+  }
+}
+#define TRACE_DECL int trace_n = 0;
+#define TRACE(role, ev, k) trace_ev(role, trace_n, ev, k)
+#else
+#define TRACE_DECL
+#define TRACE(role, ev, k)
+#endif
+
 struct BwdSm100Cfg {
   static constexpr int NSLOT = 4, LIST_MAX = 2048, NTHREADS = 384;
   static constexpr int TILE_BYTES = 128 * 128 * 2;     // 128 rows x 128 cols bf16
@@ -77,6 +95,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
   const int tid = threadIdx.x;
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
   const int lane = tid & 31;
+  TRACE_DECL
   const MaskDesc& md = p.md;
   const int off = p.Sk - p.Sq;
   const int G = p.Hq / p.Hkv;
@@ -215,8 +234,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
       const int slot = k % Cfg::NSLOT;
       ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_RFULL + slot), (uint32_t)(k / Cfg::NSLOT) & 1u, wc));
       if (!ok) break;
+      if (r == 0) TRACE(2 + pz, 10, k);   // ring slot observed full
       ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_GFULL + pz), (uint32_t)(k >> 1) & 1u, wc));
       if (!ok) break;
+      if (r == 0) TRACE(2 + pz, 12, k);   // scores observed ready
       tc_fence_after();
       const uint8_t* aux = smem + Cfg::OFF_AUX + slot * Cfg::AUX_BYTES;
       const uint32_t NEG = 0xff800000u;
@@ -421,6 +442,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
           ok = __all_sync(0xffffffffu, ok);
         }
         if (!ok) break;
+        if (lane == 0) TRACE(0, 1, k);    // slot observed empty
         if (lane == 0) {
           const uint32_t dst = sRing + slot * Cfg::SLOT_BYTES;
           const uint32_t fb = bar(Cfg::B_RFULL + slot);
@@ -449,7 +471,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
       }
     } else if (warp == 9) {
       // =========================== UMMA issuer ===========================
-      if (lane == 0 && K_items > 0) {
+      if (K_items > 0 && elect_one()) {
         constexpr uint32_t idesc_g = make_idesc(IS_BF16, 128, 64, 0, 0);
         constexpr uint32_t idesc_acc = make_idesc(IS_BF16, 128, 128, 0, 1);
         bool ok = mbar_wait(bar(Cfg::B_STAT), 0u, wc);
@@ -461,8 +483,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
         const uint64_t dRm = make_sdesc(sRing, Cfg::SUB64, 1024);    // MN-major view of a ring slot
         auto issue_g = [&](int k) {
           const int slot = k % Cfg::NSLOT, pz = k & 1;
+          TRACE(1, 20, k);                    // about to wait for the ring slot
           ok = ok && mbar_wait(bar(Cfg::B_RFULL + slot), (uint32_t)(k / Cfg::NSLOT) & 1u, wc);
           if (!ok) return;
+          TRACE(1, 21, k);                    // ring slot full
           tc_fence_after();
           const uint64_t db1 = dRk + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));
           const uint64_t db2 = db1 + (uint64_t)(Cfg::HALF_BYTES >> 4);
@@ -480,13 +504,16 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
             umma_ss(g2, dA2 + oa, db2 + ob, idesc_g, kk > 0 ? 1u : 0u);
           }
           tc_commit(bar(Cfg::B_GFULL + pz));
+          TRACE(1, 22, k);                    // G issued
         };
         issue_g(0);
         if (K_items > 1) issue_g(1);
         for (int k = 0; k < K_items && ok; ++k) {
           const int slot = k % Cfg::NSLOT, pz = k & 1;
+          TRACE(1, 23, k);                    // about to wait for T
           ok = mbar_wait(bar(Cfg::B_TFULL + pz), (uint32_t)(k >> 1) & 1u, wc);
           if (!ok) break;
+          TRACE(1, 24, k);                    // T ready
           tc_fence_after();
           const uint64_t dm1 = dRm + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));     // streamed operand 1
           const uint64_t dm2 = dm1 + (uint64_t)(Cfg::HALF_BYTES >> 4);               // streamed operand 2
@@ -505,6 +532,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
             }
           }
           tc_commit(bar(Cfg::B_REMPTY + slot));
+          TRACE(1, 25, k);                    // ACC issued
           if (k + 2 < K_items) issue_g(k + 2);
         }
         if (ok) tc_commit(bar(Cfg::B_ACC));
@@ -567,6 +595,16 @@ static int launch_bwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStr
 int bwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
   return a->dtype == FM_DTYPE_BF16 ? launch_bwd_sm100<true>(p, a, s) : launch_bwd_sm100<false>(p, a, s);
 }
+
+#ifdef FM_TRACE
+extern "C" __attribute__((visibility("default"))) int fm_debug_trace_read(int* out) {
+  cudaMemcpyFromSymbol(out, g_trace, sizeof(int) * 4 * 3 * 2048);
+  cudaMemset(nullptr, 0, 0);
+  static int zeros[4 * 3 * 2048];
+  cudaMemcpyToSymbol(g_trace, zeros, sizeof(zeros));
+  return 0;
+}
+#endif
 
 int bwd_sm100_status(int* out, bool reset) {
   int v = 0;

@@ -366,7 +366,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
     } else if (warp == 9) {
       // =========================== UMMA issuer ===========================
-      if (lane == 0) {
+      if (elect_one()) {
         constexpr uint32_t idesc_qk = make_idesc(IS_BF16, 128, 128, 0, 0);
         constexpr uint32_t idesc_pv = make_idesc(IS_BF16, 128, DV, 0, 1);
         int npv[2] = {0, 0};
