@@ -64,7 +64,7 @@ struct BwdSm100Cfg {
   static constexpr int OFF_MISC = OFF_BAR + 32 * 8;
   static constexpr int SMEM = OFF_MISC + 64 + 1024;
   static constexpr int B_STAT = 0, B_RFULL = 1, B_REMPTY = 1 + NSLOT, B_GFULL = 1 + 2 * NSLOT,
-                       B_TFULL = B_GFULL + 2, B_ACC = B_TFULL + 2, B_COUNT = B_ACC + 1;
+                       B_TFULL = B_GFULL + 2, B_GREAD = B_TFULL + 2, B_ACC = B_GREAD + 2, B_COUNT = B_ACC + 1;
   static_assert(B_COUNT <= 32, "barrier storage");
   static_assert(SMEM > 120 * 1024 && SMEM <= 227 * 1024, "one CTA per SM (512 TMEM columns)");
 };
@@ -180,7 +180,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
       mbar_init(bar(Cfg::B_RFULL + i), MODE == MODE_DQ ? 33 : 1);
       mbar_init(bar(Cfg::B_REMPTY + i), 1);
     }
-    for (int h = 0; h < 2; ++h) { mbar_init(bar(Cfg::B_GFULL + h), 1); mbar_init(bar(Cfg::B_TFULL + h), 4); }
+    for (int h = 0; h < 2; ++h) { mbar_init(bar(Cfg::B_GFULL + h), 1); mbar_init(bar(Cfg::B_TFULL + h), 4); mbar_init(bar(Cfg::B_GREAD + h), 4); }
     mbar_init(bar(Cfg::B_ACC), 1);
     fence_mbar_init();
     tma_prefetch_desc(&tm_stat1); tma_prefetch_desc(&tm_stat2);
@@ -196,8 +196,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
   const uint32_t tmem = (uint32_t)misc[0];
   const int K_items = cnt * n_heads;
   WaitCtx wc{misc + 4, global_timer_ns() + 2000000000ull};
-  // TMEM columns: G1_p at 64p, G2_p at 128+64p, accumulators at 256 (dV | dQ) and 384 (dK)
-  constexpr uint32_t C_G1 = 0, C_G2 = 128, C_ACC1 = 256, C_ACC2 = 384;
+  // TMEM columns: score buffers G1_p at 64p, G2_p at 128+64p.
+  //   DKDV: P^T_p / dS^T_p (bf16) overlay G2_p at +0 / +32; dV at 256, dK at 384.  G1_p is dead as soon as
+  //         its warpgroup has read it, so S^T of item k+2 is issued before item k is finished.
+  //   DQ:   dS (bf16) has four own 32-column buffers at 256 (index 2*((k/2)%2) + p), dQ at 384: both score
+  //         GEMMs of item k+2 are issued as soon as item k has been read.
+  constexpr uint32_t C_G1 = 0, C_G2 = 128, C_T = 256;
+  constexpr uint32_t C_ACC1 = (MODE == MODE_DKDV) ? 256 : 384, C_ACC2 = 384;
 
   if (warp < 8) {
     // =========================== compute warpgroups ===========================
@@ -241,16 +246,20 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
       tc_fence_after();
       const uint8_t* aux = smem + Cfg::OFF_AUX + slot * Cfg::AUX_BYTES;
       const uint32_t NEG = 0xff800000u;
-      // 64 score columns in two chunks of 32: the second chunk is in flight while
-      // the first is processed; the bf16 results overlay the LOWER half of the
-      // score buffers (columns already consumed by then)
+      // 64 score columns; once they are in registers the score buffers may be
+      // overwritten by the next item of this parity (signalled through g_read)
       uint32_t sr[2][32], dr[2][32];
       tmem_ld32(tG1, sr[0]); tmem_ld32(tG2, dr[0]);
-      tc_wait_ld();
       tmem_ld32(tG1 + 32, sr[1]); tmem_ld32(tG2 + 32, dr[1]);
+      tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(Cfg::B_GREAD + pz));
+      const uint32_t tT = (MODE == MODE_DKDV)
+                              ? tG2
+                              : tmem + lane_field + C_T + 32u * (uint32_t)((((k >> 1) & 1) << 1) + pz);
 #pragma unroll
       for (int hc = 0; hc < 2; ++hc) {
-        if (hc == 1) tc_wait_ld();
         uint32_t pk1[16], pk2[16];
         if (MODE == MODE_DKDV) {
           // columns are queries i0 + c; this lane is key j
@@ -276,8 +285,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
             pk1[2 * c4] = pack2<IS_BF16>(pe[0], pe[1]); pk1[2 * c4 + 1] = pack2<IS_BF16>(pe[2], pe[3]);
             pk2[2 * c4] = pack2<IS_BF16>(de[0], de[1]); pk2[2 * c4 + 1] = pack2<IS_BF16>(de[2], de[3]);
           }
-          tmem_st16(tG1 + 16 * hc, pk1);
-          tmem_st16(tG2 + 16 * hc, pk2);
+          tmem_st16(tT + 16 * hc, pk1);
+          tmem_st16(tT + 32 + 16 * hc, pk2);
         } else {
           // columns are keys jh0 + c; this lane is query i
           const int jh0 = idx * 64 + 32 * hc;
@@ -329,7 +338,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
             pk2[c] = pack2<IS_BF16>(p0 * (__uint_as_float(dr[hc][2 * c]) - dps_row),
                                     p1 * (__uint_as_float(dr[hc][2 * c + 1]) - dps_row));
           }
-          tmem_st16(tG2 + 16 * hc, pk2);
+          tmem_st16(tT + 16 * hc, pk2);
         }
       }
       tc_wait_st();
@@ -419,7 +428,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
   } else {
     if (warp == 8) {
       // =========================== producer ===========================
-      if (lane == 0 && K_items > 0) {
+      if (K_items > 0 && elect_one()) {
         mbar_arrive_expect_tx(bar(Cfg::B_STAT), 2 * Cfg::TILE_BYTES);
         const int hs = (MODE == MODE_DKDV) ? hk : hq0;
         for (int dc = 0; dc < 2; ++dc) {
@@ -443,7 +452,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
         }
         if (!ok) break;
         if (lane == 0) TRACE(0, 1, k);    // slot observed empty
-        if (lane == 0) {
+        if (elect_one()) {
           const uint32_t dst = sRing + slot * Cfg::SLOT_BYTES;
           const uint32_t fb = bar(Cfg::B_RFULL + slot);
           mbar_arrive_expect_tx(fb, Cfg::SLOT_BYTES + (MODE == MODE_DKDV ? 512 : 0));
@@ -481,7 +490,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
         const uint64_t dA2 = make_sdesc(sStat + Cfg::TILE_BYTES, 16, 1024);
         const uint64_t dRk = make_sdesc(sRing, 16, 1024);            // K-major view of a ring slot
         const uint64_t dRm = make_sdesc(sRing, Cfg::SUB64, 1024);    // MN-major view of a ring slot
-        auto issue_g = [&](int k) {
+        // part 1 of the score GEMMs of item k: what may run as soon as the warpgroup of
+        // this parity has READ the previous item (DQ: both GEMMs; DKDV: S^T only)
+        auto issue_g_early = [&](int k) {
           const int slot = k % Cfg::NSLOT, pz = k & 1;
           TRACE(1, 20, k);                    // about to wait for the ring slot
           ok = ok && mbar_wait(bar(Cfg::B_RFULL + slot), (uint32_t)(k / Cfg::NSLOT) & 1u, wc);
@@ -489,27 +500,34 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
           TRACE(1, 21, k);                    // ring slot full
           tc_fence_after();
           const uint64_t db1 = dRk + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));
-          const uint64_t db2 = db1 + (uint64_t)(Cfg::HALF_BYTES >> 4);
-          const uint32_t g1 = tmem + C_G1 + 64u * pz, g2 = tmem + C_G2 + 64u * pz;
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint64_t oa = (uint64_t)(((kk >> 2) * Cfg::SUB128 + (kk & 3) * 32) >> 4);
-            const uint64_t ob = (uint64_t)(((kk >> 2) * Cfg::SUB64 + (kk & 3) * 32) >> 4);
-            umma_ss(g1, dA1 + oa, db1 + ob, idesc_g, kk > 0 ? 1u : 0u);
+          umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(tmem + C_G1 + 64u * pz, dA1, db1, idesc_g, 0u);
+          if (MODE == MODE_DQ) {
+            umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(tmem + C_G2 + 64u * pz, dA2,
+                                                              db1 + (uint64_t)(Cfg::HALF_BYTES >> 4), idesc_g, 0u);
+            tc_commit(bar(Cfg::B_GFULL + pz));
           }
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint64_t oa = (uint64_t)(((kk >> 2) * Cfg::SUB128 + (kk & 3) * 32) >> 4);
-            const uint64_t ob = (uint64_t)(((kk >> 2) * Cfg::SUB64 + (kk & 3) * 32) >> 4);
-            umma_ss(g2, dA2 + oa, db2 + ob, idesc_g, kk > 0 ? 1u : 0u);
-          }
-          tc_commit(bar(Cfg::B_GFULL + pz));
           TRACE(1, 22, k);                    // G issued
         };
-        issue_g(0);
-        if (K_items > 1) issue_g(1);
+        // part 2 (DKDV only): dP^T overwrites the buffer that held P^T / dS^T of the
+        // previous item of this parity, so it follows that item's accumulation MMAs
+        auto issue_g_late = [&](int k) {
+          if (MODE == MODE_DKDV) {
+            const int slot = k % Cfg::NSLOT, pz = k & 1;
+            const uint64_t db2 = dRk + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4) + (Cfg::HALF_BYTES >> 4));
+            umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(tmem + C_G2 + 64u * pz, dA2, db2, idesc_g, 0u);
+            tc_commit(bar(Cfg::B_GFULL + pz));
+          }
+        };
+        issue_g_early(0); if (ok) issue_g_late(0);
+        if (K_items > 1 && ok) { issue_g_early(1); if (ok) issue_g_late(1); }
         for (int k = 0; k < K_items && ok; ++k) {
           const int slot = k % Cfg::NSLOT, pz = k & 1;
+          if (k + 2 < K_items) {
+            ok = mbar_wait(bar(Cfg::B_GREAD + pz), (uint32_t)(k >> 1) & 1u, wc);
+            if (!ok) break;
+            issue_g_early(k + 2);
+            if (!ok) break;
+          }
           TRACE(1, 23, k);                    // about to wait for T
           ok = mbar_wait(bar(Cfg::B_TFULL + pz), (uint32_t)(k >> 1) & 1u, wc);
           if (!ok) break;
@@ -518,22 +536,19 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
           const uint64_t dm1 = dRm + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));     // streamed operand 1
           const uint64_t dm2 = dm1 + (uint64_t)(Cfg::HALF_BYTES >> 4);               // streamed operand 2
           const uint32_t acc_on = k > 0 ? 1u : 0u;
-          const uint32_t t1 = tmem + C_G1 + 64u * pz, t2 = tmem + C_G2 + 64u * pz;
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t ok16 = (uint64_t)(kk * (2048 >> 4));
-            if (MODE == MODE_DKDV) {
-              // dV += P^T dO (streamed operand 2), dK += dS^T Q (streamed operand 1)
-              umma_ts(tmem + C_ACC1, t1 + 8u * kk, dm2 + ok16, idesc_acc, kk > 0 ? 1u : acc_on);
-              umma_ts(tmem + C_ACC2, t2 + 8u * kk, dm1 + ok16, idesc_acc, kk > 0 ? 1u : acc_on);
-            } else {
-              // dQ += dS K (streamed operand 1)
-              umma_ts(tmem + C_ACC1, t2 + 8u * kk, dm1 + ok16, idesc_acc, kk > 0 ? 1u : acc_on);
-            }
+          if (MODE == MODE_DKDV) {
+            // dV += P^T dO (streamed operand 2), dK += dS^T Q (streamed operand 1)
+            const uint32_t t1 = tmem + C_G2 + 64u * pz, t2 = t1 + 32u;
+            umma_ts_xn<4>(tmem + C_ACC1, t1, dm2, idesc_acc, acc_on);
+            umma_ts_xn<4>(tmem + C_ACC2, t2, dm1, idesc_acc, acc_on);
+          } else {
+            // dQ += dS K (streamed operand 1)
+            const uint32_t t2 = tmem + C_T + 32u * (uint32_t)((((k >> 1) & 1) << 1) + pz);
+            umma_ts_xn<4>(tmem + C_ACC1, t2, dm1, idesc_acc, acc_on);
           }
           tc_commit(bar(Cfg::B_REMPTY + slot));
           TRACE(1, 25, k);                    // ACC issued
-          if (k + 2 < K_items) issue_g(k + 2);
+          if (k + 2 < K_items) issue_g_late(k + 2);
         }
         if (ok) tc_commit(bar(Cfg::B_ACC));
       }

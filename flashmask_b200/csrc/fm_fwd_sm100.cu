@@ -322,7 +322,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     setmaxnreg_dec<64>();
     if (warp == 8) {
       // =========================== TMA / bounds producer ===========================
-      if (lane == 0) {
+      if (elect_one()) {
         for (int s = 0; s < 2; ++s) {
           if (cnt_s[s] > 0) {
             mbar_arrive_expect_tx(bar(Cfg::B_QFULL + s), Cfg::Q_BYTES);
@@ -337,7 +337,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       for (int i = 0; i < cnt && ok; ++i) {
         const uint32_t e = list[i];
         const int j0 = (int)(e & 0xFFFFu) * 128;
-        if (lane == 0) {
+        if (elect_one()) {
           for (int kv = 0; kv < 2 && ok; ++kv) {
             const int k = 2 * i + kv, slot = k % Cfg::NSTAGE;
             const uint32_t par = ((uint32_t)(k / Cfg::NSTAGE) & 1u) ^ 1u;
@@ -386,11 +386,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           const uint64_t da = dq0 + (uint64_t)(s * (Cfg::Q_BYTES >> 4));
           const uint64_t db = dk0 + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));
           const uint32_t dst = tmem + 128u * s;
-#pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint64_t o = (uint64_t)(((kk >> 2) * Cfg::SUB + (kk & 3) * 32) >> 4);
-            umma_ss(dst, da + o, db + o, idesc_qk, kk > 0 ? 1u : 0u);
-          }
+          umma_ss_x8<(Cfg::SUB >> 4), (Cfg::SUB >> 4)>(dst, da, db, idesc_qk, 0u);
           tc_commit(bar(Cfg::B_SFULL + s));
         };
         auto issue_pv = [&](int s, int i) {
@@ -402,9 +398,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           const uint64_t db = dv0 + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));
           const uint32_t dst = tmem + 256u + 128u * s, src = tmem + 128u * s + 64u;
           const uint32_t acc0 = npv[s] > 0 ? 1u : 0u;
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            umma_ts(dst, src + 8u * kk, db + (uint64_t)(kk * (2048 >> 4)), idesc_pv, kk > 0 ? 1u : acc0);
+          umma_ts_xn<8>(dst, src, db, idesc_pv, acc0);
           tc_commit(bar(Cfg::B_ODONE + s));
           ++npv[s];
         };

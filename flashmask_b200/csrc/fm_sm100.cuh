@@ -124,6 +124,73 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       : "memory");
 }
 
+// Eight k-steps (K = 128 elements) of D[tmem] (+)= A[smem] * B[smem], both
+// operands K-major with 128-byte swizzle, issued from ONE asm block so that
+// nothing but two 64-bit adds separates consecutive MMAs.  A_HI / B_HI: distance
+// (in 16-byte units) between the two 64-column sub-tiles of the operand.
+template <int A_HI, int B_HI>
+__device__ __forceinline__ void umma_ss_x8(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc,
+                                           uint32_t acc_first) {
+  asm volatile(
+      "{\n\t.reg .pred p, pt;\n\t.reg .b64 ta, tb;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "add.s64 ta, %1, 2;  add.s64 tb, %2, 2;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], ta, tb, %3, pt;\n\t"
+      "add.s64 ta, %1, 4;  add.s64 tb, %2, 4;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], ta, tb, %3, pt;\n\t"
+      "add.s64 ta, %1, 6;  add.s64 tb, %2, 6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], ta, tb, %3, pt;\n\t"
+      "add.s64 ta, %1, %5; add.s64 tb, %2, %6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], ta, tb, %3, pt;\n\t"
+      "add.s64 ta, %1, %7; add.s64 tb, %2, %8;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], ta, tb, %3, pt;\n\t"
+      "add.s64 ta, %1, %9; add.s64 tb, %2, %10;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], ta, tb, %3, pt;\n\t"
+      "add.s64 ta, %1, %11; add.s64 tb, %2, %12;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], ta, tb, %3, pt;\n\t}"
+      ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(acc_first),
+        "n"(A_HI), "n"(B_HI), "n"(A_HI + 2), "n"(B_HI + 2), "n"(A_HI + 4), "n"(B_HI + 4), "n"(A_HI + 6), "n"(B_HI + 6)
+      : "memory");
+}
+
+// NK k-steps of D[tmem] (+)= A[tmem] * B[smem]: A advances 8 columns (16 bf16)
+// and the MN-major B 16 rows (2048 bytes) per step.
+template <int NK>
+__device__ __forceinline__ void umma_ts_xn(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc,
+                                           uint32_t acc_first) {
+  static_assert(NK == 4 || NK == 8, "4 or 8 k-steps");
+  asm volatile(
+      "{\n\t.reg .pred p, pt;\n\t.reg .b64 tb;\n\t.reg .b32 ta;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "add.u32 ta, %1, 8;  add.s64 tb, %2, 128;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], tb, %3, pt;\n\t"
+      "add.u32 ta, %1, 16; add.s64 tb, %2, 256;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], tb, %3, pt;\n\t"
+      "add.u32 ta, %1, 24; add.s64 tb, %2, 384;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], tb, %3, pt;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc_first)
+      : "memory");
+  if constexpr (NK == 8) {
+    asm volatile(
+        "{\n\t.reg .pred pt;\n\t.reg .b64 tb;\n\t.reg .b32 ta;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "add.u32 ta, %1, 32; add.s64 tb, %2, 512;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], tb, %3, pt;\n\t"
+        "add.u32 ta, %1, 40; add.s64 tb, %2, 640;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], tb, %3, pt;\n\t"
+        "add.u32 ta, %1, 48; add.s64 tb, %2, 768;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], tb, %3, pt;\n\t"
+        "add.u32 ta, %1, 56; add.s64 tb, %2, 896;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], tb, %3, pt;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(idesc)
+        : "memory");
+  }
+}
+
 // 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread
 // (thread t of warp w reads TMEM lane 32*(w%4)+t).
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
