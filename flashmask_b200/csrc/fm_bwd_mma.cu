@@ -384,16 +384,20 @@ __global__ void __launch_bounds__(256) bwd_dq_mma_kernel(const AttnKParams p) {
 // ---------------------------------------------------------------------------
 // preprocess + dsink
 // ---------------------------------------------------------------------------
-template <bool IS_BF16>
+// dPsum[b,h,i] = sum_c O[b,i,h,c] * dO[b,i,h,c]; lse_log2 = LSE * log2(e) (-inf -> 0).
+// LPR lanes share one row (each lane owns 8-element chunks), so a warp covers
+// 32 / LPR rows per pass and every lane has a 16-byte load in flight.
+template <bool IS_BF16, int LPR>
 __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const AttnKParams p) {
+  constexpr int RPW = 32 / LPR;                       // rows per warp
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = blockIdx.x * 8 + warp, hq = blockIdx.y, b = blockIdx.z;
-  if (row >= p.Sq_r) return;
+  const int sub = lane / LPR, ln = lane % LPR;
+  const int row = (blockIdx.x * 8 + warp) * RPW + sub, hq = blockIdx.y, b = blockIdx.z;
   float acc = 0.f, lse2 = 0.f;
   if (row < p.Sq) {
     const uint16_t* o = reinterpret_cast<const uint16_t*>(p.o) + b * p.o_b + (int64_t)row * p.o_s + hq * p.o_h;
     const uint16_t* d_o = reinterpret_cast<const uint16_t*>(p.d_o) + b * p.do_b + (int64_t)row * p.do_s + hq * p.do_h;
-    for (int c = lane * 8; c < p.dv_dim; c += 256) {
+    for (int c = ln * 8; c < p.dv_dim; c += LPR * 8) {
       const uint4 a = *reinterpret_cast<const uint4*>(o + c);
       const uint4 g = *reinterpret_cast<const uint4*>(d_o + c);
       const uint32_t av[4] = {a.x, a.y, a.z, a.w}, gv[4] = {g.x, g.y, g.z, g.w};
@@ -410,12 +414,14 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const AttnKParams p
         acc += x.x * y.x + x.y * y.y;
       }
     }
-#pragma unroll
-    for (int o2 = 16; o2; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
-    const float l = p.lse[((int64_t)b * p.Hq + hq) * p.Sq + row];
-    lse2 = (l == -INFINITY) ? 0.f : l * kLog2e;
+    if (ln == 0) {
+      const float l = p.lse[((int64_t)b * p.Hq + hq) * p.Sq + row];
+      lse2 = (l == -INFINITY) ? 0.f : l * kLog2e;
+    }
   }
-  if (lane == 0) {
+#pragma unroll
+  for (int o2 = LPR / 2; o2; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
+  if (ln == 0 && row < p.Sq_r) {
     const int64_t at = ((int64_t)b * p.Hq + hq) * p.Sq_r + row;
     p.dpsum[at] = acc;
     p.lse_log2[at] = lse2;
@@ -475,10 +481,19 @@ int bwd_mma_tile_shape(int d, int dv, int* tile_m, int* tile_n) {
   return FM_ERR_UNSUPPORTED;
 }
 
+template <int LPR>
+static void launch_preprocess(const AttnKParams& p, int dtype, cudaStream_t s) {
+  constexpr int rows_per_block = 8 * (32 / LPR);
+  dim3 grid((p.Sq_r + rows_per_block - 1) / rows_per_block, p.Hq, p.B);
+  if (dtype == FM_DTYPE_BF16) bwd_preprocess_kernel<true, LPR><<<grid, 256, 0, s>>>(p);
+  else bwd_preprocess_kernel<false, LPR><<<grid, 256, 0, s>>>(p);
+}
+
 int bwd_preprocess_launch(const AttnKParams& p, int dtype, cudaStream_t s) {
-  dim3 grid((p.Sq_r + 7) / 8, p.Hq, p.B);
-  if (dtype == FM_DTYPE_BF16) bwd_preprocess_kernel<true><<<grid, 256, 0, s>>>(p);
-  else bwd_preprocess_kernel<false><<<grid, 256, 0, s>>>(p);
+  const int chunks = p.dv_dim / 8;
+  if (chunks <= 8) launch_preprocess<8>(p, dtype, s);
+  else if (chunks <= 16) launch_preprocess<16>(p, dtype, s);
+  else launch_preprocess<32>(p, dtype, s);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }

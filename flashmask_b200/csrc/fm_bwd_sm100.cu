@@ -112,6 +112,30 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
   const int n_heads = (MODE == MODE_DKDV) ? G : 1;
 
   if (tid == 0) misc[4] = 0;
+  if (warp == 8 && lane == 0) {
+    mbar_init(bar(Cfg::B_STAT), 1);
+    for (int i = 0; i < Cfg::NSLOT; ++i) {
+      mbar_init(bar(Cfg::B_RFULL + i), MODE == MODE_DQ ? 33 : 1);
+      mbar_init(bar(Cfg::B_REMPTY + i), 1);
+    }
+    for (int h = 0; h < 2; ++h) { mbar_init(bar(Cfg::B_GFULL + h), 1); mbar_init(bar(Cfg::B_TFULL + h), 4); mbar_init(bar(Cfg::B_GREAD + h), 4); }
+    mbar_init(bar(Cfg::B_ACC), 1);
+    fence_mbar_init();
+    // the stationary tiles are requested right away: the loads overlap with the list build
+    mbar_arrive_expect_tx(bar(Cfg::B_STAT), 2 * Cfg::TILE_BYTES);
+    {
+      const int hs = (MODE == MODE_DKDV) ? hk : hq0;
+      for (int dc = 0; dc < 2; ++dc) {
+        tma_load_4d(sStat + dc * Cfg::SUB128, &tm_stat1, bar(Cfg::B_STAT), dc * 64, hs, row0, b);
+        tma_load_4d(sStat + Cfg::TILE_BYTES + dc * Cfg::SUB128, &tm_stat2, bar(Cfg::B_STAT), dc * 64, hs, row0, b);
+      }
+    }
+    tma_prefetch_desc(&tm_str1); tma_prefetch_desc(&tm_str2);
+  }
+  if (warp == 9) {
+    tmem_alloc(sbase + Cfg::OFF_MISC, 512);
+    tmem_relinquish();
+  }
   if (warp == 10) {
     int cnt = 0;
     if (MODE == MODE_DKDV) {
@@ -150,11 +174,17 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
     }
     if (lane == 0) misc[1] = min(cnt, Cfg::LIST_MAX);
   }
+  tc_fence_before();
   __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = (uint32_t)misc[0];
   const int cnt = misc[1];
+  WaitCtx wc{misc + 4, global_timer_ns() + 2000000000ull};
   if (cnt == 0) {
-    // this tile's gradients are all zero: store them and leave before touching
-    // barriers or TMEM
+    // this tile's gradients are all zero: store them; the stationary loads already
+    // in flight are awaited and the tensor memory is returned before leaving
+    if (warp == 8 && lane == 0) mbar_wait(bar(Cfg::B_STAT), 0u, wc);
+    if (warp == 9) tmem_dealloc(tmem, 512);
     if (MODE == MODE_DKDV) {
       uint16_t* gk = reinterpret_cast<uint16_t*>(p.dk) + b * p.dk_b + (int64_t)row0 * p.dk_s + hk * p.dk_h;
       uint16_t* gv = reinterpret_cast<uint16_t*>(p.dv) + b * p.dv_b + (int64_t)row0 * p.dv_s + hk * p.dv_h;
@@ -174,33 +204,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
     }
     return;
   }
-  if (warp == 8 && lane == 0) {
-    mbar_init(bar(Cfg::B_STAT), 1);
-    for (int i = 0; i < Cfg::NSLOT; ++i) {
-      mbar_init(bar(Cfg::B_RFULL + i), MODE == MODE_DQ ? 33 : 1);
-      mbar_init(bar(Cfg::B_REMPTY + i), 1);
-    }
-    for (int h = 0; h < 2; ++h) { mbar_init(bar(Cfg::B_GFULL + h), 1); mbar_init(bar(Cfg::B_TFULL + h), 4); mbar_init(bar(Cfg::B_GREAD + h), 4); }
-    mbar_init(bar(Cfg::B_ACC), 1);
-    fence_mbar_init();
-    tma_prefetch_desc(&tm_stat1); tma_prefetch_desc(&tm_stat2);
-    tma_prefetch_desc(&tm_str1); tma_prefetch_desc(&tm_str2);
-  }
-  if (warp == 9) {
-    tmem_alloc(sbase + Cfg::OFF_MISC, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = (uint32_t)misc[0];
   const int K_items = cnt * n_heads;
-  WaitCtx wc{misc + 4, global_timer_ns() + 2000000000ull};
   // TMEM columns: score buffers G1_p at 64p, G2_p at 128+64p.
   //   DKDV: P^T_p / dS^T_p (bf16) overlay G2_p at +0 / +32; dV at 256, dK at 384.  G1_p is dead as soon as
   //         its warpgroup has read it, so S^T of item k+2 is issued before item k is finished.
-  //   DQ:   dS (bf16) has four own 32-column buffers at 256 (index 2*((k/2)%2) + p), dQ at 384: both score
-  //         GEMMs of item k+2 are issued as soon as item k has been read.
+  //   DQ:   dS (bf16) has four own 32-column buffers at 256 (index 2*((k/2)%2) + p), dQ at 384.
   constexpr uint32_t C_G1 = 0, C_G2 = 128, C_T = 256;
   constexpr uint32_t C_ACC1 = (MODE == MODE_DKDV) ? 256 : 384, C_ACC2 = 384;
 
@@ -428,14 +436,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
   } else {
     if (warp == 8) {
       // =========================== producer ===========================
-      if (K_items > 0 && elect_one()) {
-        mbar_arrive_expect_tx(bar(Cfg::B_STAT), 2 * Cfg::TILE_BYTES);
-        const int hs = (MODE == MODE_DKDV) ? hk : hq0;
-        for (int dc = 0; dc < 2; ++dc) {
-          tma_load_4d(sStat + dc * Cfg::SUB128, &tm_stat1, bar(Cfg::B_STAT), dc * 64, hs, row0, b);
-          tma_load_4d(sStat + Cfg::TILE_BYTES + dc * Cfg::SUB128, &tm_stat2, bar(Cfg::B_STAT), dc * 64, hs, row0, b);
-        }
-      }
       bool ok = true;
       for (int k = 0; k < K_items && ok; ++k) {
         const uint32_t e = list[k % cnt];
@@ -490,8 +490,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
         const uint64_t dA2 = make_sdesc(sStat + Cfg::TILE_BYTES, 16, 1024);
         const uint64_t dRk = make_sdesc(sRing, 16, 1024);            // K-major view of a ring slot
         const uint64_t dRm = make_sdesc(sRing, Cfg::SUB64, 1024);    // MN-major view of a ring slot
-        // part 1 of the score GEMMs of item k: what may run as soon as the warpgroup of
-        // this parity has READ the previous item (DQ: both GEMMs; DKDV: S^T only)
+        // part 1 of the score GEMMs of item k: the first one (S or S^T) runs as soon as the
+        // warpgroup of this parity has READ the previous item out of the score buffers
         auto issue_g_early = [&](int k) {
           const int slot = k % Cfg::NSLOT, pz = k & 1;
           TRACE(1, 20, k);                    // about to wait for the ring slot
@@ -501,17 +501,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
           tc_fence_after();
           const uint64_t db1 = dRk + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));
           umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(tmem + C_G1 + 64u * pz, dA1, db1, idesc_g, 0u);
-          if (MODE == MODE_DQ) {
-            umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(tmem + C_G2 + 64u * pz, dA2,
-                                                              db1 + (uint64_t)(Cfg::HALF_BYTES >> 4), idesc_g, 0u);
-            tc_commit(bar(Cfg::B_GFULL + pz));
-          }
+
           TRACE(1, 22, k);                    // G issued
         };
-        // part 2 (DKDV only): dP^T overwrites the buffer that held P^T / dS^T of the
-        // previous item of this parity, so it follows that item's accumulation MMAs
+        // part 2: the second score GEMM (dP or dP^T) follows the accumulation MMAs of the
+        // previous item of this parity (in DKDV mode it overwrites the buffer that held
+        // that item's P^T / dS^T)
         auto issue_g_late = [&](int k) {
-          if (MODE == MODE_DKDV) {
+          {
             const int slot = k % Cfg::NSLOT, pz = k & 1;
             const uint64_t db2 = dRk + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4) + (Cfg::HALF_BYTES >> 4));
             umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(tmem + C_G2 + 64u * pz, dA2, db2, idesc_g, 0u);

@@ -80,6 +80,28 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int off = p.Sk - p.Sq;
 
   if (tid == 0) misc[4] = 0;
+  if (warp == 8 && lane == 0) {
+    mbar_init(bar(Cfg::B_QFULL + 0), 1); mbar_init(bar(Cfg::B_QFULL + 1), 1);
+    for (int i = 0; i < Cfg::NSTAGE; ++i) { mbar_init(bar(Cfg::B_KVFULL + i), 1); mbar_init(bar(Cfg::B_KVEMPTY + i), 1); }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(Cfg::B_SFULL + s), 1); mbar_init(bar(Cfg::B_PFULL + s), 128); mbar_init(bar(Cfg::B_ODONE + s), 1);
+    }
+    for (int i = 0; i < Cfg::NBND; ++i) { mbar_init(bar(Cfg::B_BNDFULL + i), 32); mbar_init(bar(Cfg::B_BNDEMPTY + i), 256); }
+    fence_mbar_init();
+    // both Q sub-tiles are requested right away: the loads overlap with the
+    // list build (rows past the end of the sequence arrive as zeros)
+    for (int s = 0; s < 2; ++s) {
+      mbar_arrive_expect_tx(bar(Cfg::B_QFULL + s), Cfg::Q_BYTES);
+      for (int dc = 0; dc < D / 64; ++dc)
+        tma_load_4d(sQ + s * Cfg::Q_BYTES + dc * Cfg::SUB, &tm_q, bar(Cfg::B_QFULL + s), dc * 64, hq,
+                    ms + 128 * s, b);
+    }
+    tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 9) {
+    tmem_alloc(sbase + Cfg::OFF_MISC, 512);
+    tmem_relinquish();
+  }
   if (warp == 10) {
     // surviving K tiles, right to left, with the flags of both sub-tiles
     const int nb = (p.Sk + 127) / 128;
@@ -104,11 +126,21 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
     if (lane == 0) { misc[1] = min(cnt, Cfg::LIST_MAX); misc[2] = c0; misc[3] = c1; }
   }
+  tc_fence_before();
   __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = (uint32_t)misc[0];
   const int cnt = misc[1];
+  WaitCtx wc{misc + 4, global_timer_ns() + 2000000000ull};
   if (cnt == 0) {
     // nothing visible for these 256 rows: write O = 0 and LSE = -inf (sink
-    // present: LSE = sink) and leave before touching barriers or TMEM
+    // present: LSE = sink); the Q loads already in flight are awaited and the
+    // tensor memory is returned before leaving
+    if (warp == 8 && lane == 0) {
+      mbar_wait(bar(Cfg::B_QFULL + 0), 0u, wc);
+      mbar_wait(bar(Cfg::B_QFULL + 1), 0u, wc);
+    }
+    if (warp == 9) tmem_dealloc(tmem, 512);
     uint16_t* go = reinterpret_cast<uint16_t*>(p.o) + b * p.o_b + (int64_t)ms * p.o_s + hq * p.o_h;
     for (int x = tid; x < 256 * (DV / 8); x += Cfg::NTHREADS) {
       const int rr = x / (DV / 8), cc = x % (DV / 8);
@@ -119,26 +151,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (ms + rr < p.Sq) p.lse[((int64_t)b * p.Hq + hq) * p.Sq + ms + rr] = empty_lse;
     return;
   }
-  if (warp == 8 && lane == 0) {
-    mbar_init(bar(Cfg::B_QFULL + 0), 1); mbar_init(bar(Cfg::B_QFULL + 1), 1);
-    for (int i = 0; i < Cfg::NSTAGE; ++i) { mbar_init(bar(Cfg::B_KVFULL + i), 1); mbar_init(bar(Cfg::B_KVEMPTY + i), 1); }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(bar(Cfg::B_SFULL + s), 1); mbar_init(bar(Cfg::B_PFULL + s), 128); mbar_init(bar(Cfg::B_ODONE + s), 1);
-    }
-    for (int i = 0; i < Cfg::NBND; ++i) { mbar_init(bar(Cfg::B_BNDFULL + i), 32); mbar_init(bar(Cfg::B_BNDEMPTY + i), 256); }
-    fence_mbar_init();
-    tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
-  }
-  if (warp == 9) {
-    tmem_alloc(sbase + Cfg::OFF_MISC, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = (uint32_t)misc[0];
   const int cnt_s[2] = {misc[2], misc[3]};
-  WaitCtx wc{misc + 4, global_timer_ns() + 2000000000ull};
 
   if (warp < 8) {
     // =========================== softmax warpgroups ===========================
@@ -322,16 +335,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     setmaxnreg_dec<64>();
     if (warp == 8) {
       // =========================== TMA / bounds producer ===========================
-      if (elect_one()) {
-        for (int s = 0; s < 2; ++s) {
-          if (cnt_s[s] > 0) {
-            mbar_arrive_expect_tx(bar(Cfg::B_QFULL + s), Cfg::Q_BYTES);
-            for (int dc = 0; dc < D / 64; ++dc)
-              tma_load_4d(sQ + s * Cfg::Q_BYTES + dc * Cfg::SUB, &tm_q, bar(Cfg::B_QFULL + s), dc * 64, hq,
-                          ms + 128 * s, b);
-          }
-        }
-      }
       int nbnd = 0;
       bool ok = true;
       for (int i = 0; i < cnt && ok; ++i) {
@@ -364,6 +367,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ++nbnd;
         }
       }
+      // a sub-tile without work never consumed its Q load: make sure it has landed
+      if (ok && lane == 0) { mbar_wait(bar(Cfg::B_QFULL + 0), 0u, wc); mbar_wait(bar(Cfg::B_QFULL + 1), 0u, wc); }
     } else if (warp == 9) {
       // =========================== UMMA issuer ===========================
       if (elect_one()) {
