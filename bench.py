@@ -359,11 +359,15 @@ def main():
     peak_tf = peaks.get("bf16_tflops_sustained") or 1400.0
     peak_src = "measured (sustained cuBLAS bf16)" if peaks else "fallback"
     dom = "bwd" if ms_bwd >= ms_fwd else "fwd"
+    # DRAM bytes per launch of this workload from one ncu capture (backward = preprocess + dK/dV + dQ kernels)
+    NCU_DRAM_BYTES = {"fwd": 306.7e6, "bwd": 1198.0e6}
     dom_flops, dom_ms = (bwd_flops, ms_bwd) if dom == "bwd" else (fwd_flops, ms_fwd)
     ach = dom_flops / (dom_ms * 1e-3) / 1e12
     roofline = {"bound": "tensor", "kernel": "fm_bwd (preprocess + dK/dV + dQ kernels)" if dom == "bwd" else "fm_fwd kernel",
                 "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / peak_tf,
-                "peak_source": peak_src, "traffic": None,
+                "peak_source": peak_src,
+                "traffic": NCU_DRAM_BYTES[dom], "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, "
+                "one capture of this workload (profiles/fwd_bwd_sm100_kernels_causal_doc_8k_gqa_ncu_full.md)",
                 "fwd_ms": ms_fwd, "bwd_ms": ms_bwd, "mask_prep_ms": ms_prep,
                 "fwd_tflops": fwd_flops / (ms_fwd * 1e-3) / 1e12,
                 "bwd_tflops": bwd_flops / (ms_bwd * 1e-3) / 1e12}
