@@ -59,6 +59,7 @@ SIGNATURES = {
     "fm_bwd_static_scratch": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "fm_cp_chunk_workload": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "fm_cp_partition_heap": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "fm_cp_partition_ipo": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "fm_cp_rerank": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                C.c_int, C.c_int, C.c_void_p]),
     "fm_cp_localize": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]),

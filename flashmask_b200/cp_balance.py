@@ -19,7 +19,7 @@ import torch
 from . import _lib
 from .ops import _stream, prepare_mask
 
-__all__ = ["get_q_workload", "assign_tasks_heap", "indices_rerank_cuda", "indices_to_chunks_cuda",
+__all__ = ["get_q_workload", "assign_tasks_heap", "assign_tasks_ipo", "cp_balance_ipo_solve", "indices_rerank_cuda", "indices_to_chunks_cuda",
            "balance_flashmask_input", "scatter_by_buckets", "dual_chunk_buckets"]
 
 
@@ -69,6 +69,36 @@ def assign_tasks_heap(tasks, num_buckets: int):
     return buckets, weights, cuts
 
 
+def cp_balance_ipo_solve(weights, num_buckets: int):
+    """``(assign, max_load)``: ``assign`` is int32 ``[num_buckets, N // num_buckets]`` task indices.
+    Reference: cp_balance_ipo_solve, flashmask/cp_balance/cp_balance_cuda_kernels.py, over
+    CpBalanceSolver::solve_to (csrc/cp_balance_fast.hpp:86-100)."""
+    w = np.ascontiguousarray(weights, dtype=np.int32)
+    n = int(w.shape[0])
+    assign = np.empty((int(num_buckets), n // int(num_buckets)), dtype=np.int32)
+    best = C.c_int64(0)
+    _lib.check(_lib.load().fm_cp_partition_ipo(w.ctypes.data, n, int(num_buckets), assign.ctypes.data,
+                                               C.addressof(best)), "fm_cp_partition_ipo")
+    return assign, int(best.value)
+
+
+def assign_tasks_ipo(tasks, num_buckets: int):
+    """Iterative pairwise/triple optimal partition with the interface of
+    ``assign_tasks_heap``; falls back to the heap when ``N == 0``, ``N > 512`` or
+    ``N % num_buckets != 0`` (reference: flashmask/cp_balance/cp_balance.py:177-228)
+    and, where the reference solver's tables end, when ``num_buckets > 32``."""
+    tasks = np.asarray(tasks.cpu() if hasattr(tasks, "cpu") else tasks)
+    n = len(tasks)
+    if n == 0 or n > 512 or n % num_buckets != 0 or num_buckets > 32:
+        return assign_tasks_heap(tasks, num_buckets)
+    assign, _ = cp_balance_ipo_solve(tasks[:, 0], num_buckets)
+    buckets = [sorted(((int(tasks[i, 0]), int(tasks[i, 1])) for i in row), key=lambda x: x[1]) for row in assign]
+    weights = [sum(x[0] for x in b) for b in buckets]
+    all_idx = sorted(i for b in buckets for _, i in b)
+    cuts = sum(1 for i in range(1, len(all_idx)) if all_idx[i] != all_idx[i - 1] + 1)
+    return buckets, weights, cuts
+
+
 def indices_rerank_cuda(startend_row_indices: torch.Tensor, indices: torch.Tensor,
                         balance_chunk_size: int = 2048) -> torch.Tensor:
     """Gather the key axis into chunk order ``indices``
@@ -105,13 +135,11 @@ def balance_flashmask_input(startend_row_indices: torch.Tensor, cp_size: int, cp
     and dO are scattered with the same plan (``scatter_by_buckets``).  The local
     mask has its key axis in rank order over ALL ranks and its row bounds in
     this rank's local row space; run it with ``causal=False``."""
-    if use_ipo:
-        raise NotImplementedError("the IPO repartition solver is not built yet; use the LPT heap (use_ipo=False)")
     workload = get_q_workload(startend_row_indices, balance_chunk_size, q_block_size, k_block_size)
     # one host synchronisation, as in the reference (cp_balance.py:400)
     tasks = workload[:, 0].reshape(-1, 2).cpu().numpy() if workload.shape[1] == 1 else \
         _sum_mask_heads(workload).cpu().numpy()
-    buckets, _, _ = assign_tasks_heap(tasks, cp_size)
+    buckets, _, _ = (assign_tasks_ipo if use_ipo else assign_tasks_heap)(tasks, cp_size)
     order = torch.tensor([i for b in buckets for _, i in b], dtype=torch.int32)
     reranked = indices_rerank_cuda(startend_row_indices, order, balance_chunk_size)
     local = torch.tensor([i for _, i in buckets[cp_rank]], dtype=torch.int32)

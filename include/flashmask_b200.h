@@ -196,6 +196,18 @@ FM_API int fm_cp_chunk_workload(const int32_t* valid_cnt, int B, int Hm, int Tq,
  * Replaces assign_tasks_heap (flashmask/cp_balance/cp_balance.py:96-174). */
 FM_API int fm_cp_partition_heap(const int32_t* weights, int n, int n_buckets, int32_t* bucket_of);
 
+/* Iterative pairwise / triple optimal repartition of n weighted tasks into
+ * n_buckets buckets of exactly n / n_buckets tasks each (HOST pointers):
+ * assign[j * (n / n_buckets) + t] = index of the t-th task of bucket j, in the
+ * solver's order; *max_load (may be NULL) = the heaviest bucket.  Requires
+ * n % n_buckets == 0, n <= 512, n_buckets <= 32 (FM_ERR_UNSUPPORTED beyond: the
+ * caller falls back to the heap partition, as assign_tasks_ipo does).
+ * Replaces CpBalanceSolver::solve_to (flashmask/cp_balance/csrc/cp_balance_fast.hpp:86-100,
+ * core :416-581) behind cp_balance_ipo_solve (cp_balance_cuda_kernels.py) and
+ * assign_tasks_ipo (flashmask/cp_balance/cp_balance.py:177-228). */
+FM_API int fm_cp_partition_ipo(const int32_t* weights, int n, int n_buckets, int32_t* assign,
+                               int64_t* max_load);
+
 /* Gather the key axis of the mask into chunk order `chunk_idx`:
  * out[b,h,c*C + r,:] = mask[b,h,chunk_idx[c]*C + r,:].
  * Replaces indices_rerank_kernel (csrc/cp_balance_bridge.cu:185-216). */

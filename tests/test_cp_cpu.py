@@ -59,6 +59,58 @@ def test_reference_ipo_solver_oracle_if_built():
         assert sorted(out.tolist()) == list(range(64))
 
 
+def test_ipo_partition_matches_reference_vectors():
+    """fm_cp_partition_ipo against assignments computed by the reference's own solver
+    (tests/golden/make_ipo_golden.py): the same chunk in the same slot of the same rank."""
+    g = np.load(os.path.join(ROOT, "tests", "golden", "ipo_partition.npz"))
+    for k in range(int(g["n_cases"])):
+        w, m = g[f"w_{k}"], int(g[f"m_{k}"])
+        a, best = cp_balance.cp_balance_ipo_solve(w, m)
+        assert best == int(g[f"best_{k}"]), k
+        assert np.array_equal(a, g[f"a_{k}"]), k
+        assert best == max(int(w[row].sum()) for row in a)
+
+
+def test_ipo_partition_matches_reference_solver_if_built():
+    path = os.path.join(ROOT, "oracle", "_ref", "libcpsolver_ref.so")
+    if not os.path.exists(path):
+        pytest.skip("oracle/_ref not built (needs the reference checkout)")
+    lib = ctypes.CDLL(path)
+    rng = np.random.default_rng(11)
+    for m, per in [(2, 6), (4, 8), (8, 8), (8, 10), (4, 11), (16, 3), (5, 7)]:
+        for hi in (6, 300, 100000):
+            n = m * per
+            w = rng.integers(0, hi, size=n).astype(np.int32)
+            ref = np.zeros((m, per), dtype=np.int32)
+            best_ref = lib.ref_ipo_solve(w.ctypes.data, n, m, ref.ctypes.data)
+            a, best = cp_balance.cp_balance_ipo_solve(w, m)
+            assert best == best_ref and np.array_equal(a, ref)
+
+
+def test_assign_tasks_ipo_interface_and_fallbacks():
+    rng = np.random.default_rng(5)
+    w = rng.integers(1, 3000, size=64)
+    tasks = np.stack([w, np.arange(64)], axis=1).astype(np.int32)
+    buckets, weights, cuts = cp_balance.assign_tasks_ipo(tasks, 8)
+    heap = cp_balance.assign_tasks_heap(tasks, 8)
+    assert sorted(i for b in buckets for _, i in b) == list(range(64))
+    assert all(len(b) == 8 and b == sorted(b, key=lambda x: x[1]) for b in buckets)
+    assert weights == [sum(x[0] for x in b) for b in buckets]
+    lower = max(-(-int(w.sum()) // 8), int(w.max()))
+    assert lower <= max(weights) <= max(heap[1])
+    # the cases the reference hands to the heap: n not a multiple of the ranks, n > 512, no tasks
+    for n, m in [(10, 4), (1024, 8)]:
+        t = np.stack([rng.integers(0, 99, size=n), np.arange(n)], axis=1).astype(np.int32)
+        assert cp_balance.assign_tasks_ipo(t, m) == cp_balance.assign_tasks_heap(t, m)
+    assert cp_balance.assign_tasks_ipo(np.zeros((0, 2), np.int32), 4)[1] == [0, 0, 0, 0]
+    # the C entry point refuses what it cannot solve instead of guessing
+    lib = cp_balance._lib.load()
+    big = np.ones(1024, np.int32)
+    out = np.zeros(1024, np.int32)
+    assert lib.fm_cp_partition_ipo(big.ctypes.data, 1024, 8, out.ctypes.data, None) == 2
+    assert lib.fm_cp_partition_ipo(big.ctypes.data, 10, 4, out.ctypes.data, None) == 1
+
+
 def test_plan_pairs_are_consistent():
     rng = np.random.default_rng(3)
     for world in (2, 4, 8):

@@ -171,3 +171,23 @@ def test_skipped_shards_and_balance_quality():
     loads = [sum(w for w, _ in b) for b in buckets]
     assert max(loads) <= sum(loads) / cpn * 4 / 3 + wl.max()
     assert sum(map(sum, need)) < cpn * cpn      # something was skipped
+
+
+@pytest.mark.parametrize("cpn", [2, 4, 8])
+def test_ipo_partition_end_to_end(cpn):
+    """use_ipo=True: same contract as the heap path (every chunk once, equal counts, local
+    masks consistent with the CPU localisation), never a heavier heaviest rank."""
+    S, chunk = 16384, 512
+    rng = np.random.default_rng(40 + cpn)
+    lens = W.lognormal_doc_lengths(rng, S, np.log(S / 16), 1.5, 64, S // 2)
+    idx_np = W.causal_document_noncausal_form(1, S, S, lens)[0]
+    idx = torch.from_numpy(np.ascontiguousarray(idx_np)).cuda()
+    heap_buckets = cp_balance.balance_flashmask_input(idx, cpn, 0, balance_chunk_size=chunk)[1]
+    for r in range(cpn):
+        local, buckets = cp_balance.balance_flashmask_input(idx, cpn, r, balance_chunk_size=chunk, use_ipo=True)
+        order = [i for b in buckets for _, i in b]
+        ref_local = ocp.localize(ocp.rerank(idx_np, order, chunk), [i for _, i in buckets[r]], chunk)
+        assert np.array_equal(local.cpu().numpy(), ref_local), r
+    assert sorted(order) == list(range(S // chunk)) and all(len(b) == S // chunk // cpn for b in buckets)
+    load = lambda bs: max(sum(w for w, _ in b) for b in bs)
+    assert load(buckets) <= load(heap_buckets)
