@@ -304,9 +304,15 @@ def main():
         info_f = fm.prepare_mask(idx, w.Sq, w.causal, ftm, ftn) if idx is not None else None
         info_b = info_f if (info_f is None or btn == ftn) else fm.prepare_mask(idx, w.Sq, w.causal, btm, btn)
         out, lse = fm._flash_attn_fwd(q, k, v, idx, causal=w.causal, mask_info=info_f)
-        return fm._flash_attn_bwd(q, k, v, out, do, lse, idx, causal=w.causal, mask_info=info_b)
+        res = fm._flash_attn_bwd(q, k, v, out, do, lse, idx, causal=w.causal, mask_info=info_b)
+        # launch-order tables are built once per mask info, i.e. once per step here (1 kernel each)
+        n_launch["order"] = sum(t is not None for i in {id(info_f): info_f, id(info_b): info_b}.values()
+                                if i is not None for t in i.orders.values())
+        return res
 
-    launches_per_step = (1 if idx is not None else 0) * (1 if btn == ftn else 2) + 1 + 3
+    # mask scan (+1 if fwd and bwd tile widths differ) + launch-order tables + forward + (preprocess, dK/dV, dQ)
+    launches_per_step = lambda: ((1 if idx is not None else 0) * (1 if btn == ftn else 2) +
+                                 n_launch.get("order", 0) + 1 + 3)
 
     def barrier():
         if world > 1:
@@ -414,7 +420,7 @@ def main():
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": config, "clocks": clocks,
             "e2e": e2e,
-            "gpu_launches": launches_per_step * args.steps, "roofline": roofline,
+            "gpu_launches": launches_per_step() * args.steps, "roofline": roofline,
             "frac_of_peak_fwd_bwd": value / world / peak_tf,
             "tokens_per_s": world * w.B * w.Sq / (ms_step * 1e-3)}
     if world == 1 and not args.no_e2e and args.workload is None:

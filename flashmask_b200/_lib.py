@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libflashmask_b200.so")
 
 FM_OK = 0
 FM_DTYPE_BF16, FM_DTYPE_FP16 = 0, 1
+FM_ORDER_FWD, FM_ORDER_BWD_DQ, FM_ORDER_BWD_DKDV = 0, 1, 2
 TILE_SKIP, TILE_PARTIAL, TILE_FULL = 0, 1, 2
 
 I64x3 = C.c_int64 * 3
@@ -37,6 +38,7 @@ class AttnArgs(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("q_stride", I64x3), ("k_stride", I64x3), ("v_stride", I64x3), ("o_stride", I64x3),
         ("do_stride", I64x3), ("dq_stride", I64x3), ("dk_stride", I64x3), ("dv_stride", I64x3),
+        ("fwd_order", C.c_void_p), ("dq_order", C.c_void_p), ("dkdv_order", C.c_void_p),
     ]
 
 
@@ -52,6 +54,8 @@ SIGNATURES = {
     "fm_fwd_tile_shape": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "fm_bwd_tile_shape": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "fm_fwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
+    "fm_launch_order_ints": (C.c_int64, [C.POINTER(AttnArgs), C.c_int]),
+    "fm_launch_order": (C.c_int, [C.POINTER(AttnArgs), C.c_int, C.c_void_p, C.c_void_p]),
     "fm_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(AttnArgs)]),
     "fm_bwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "fm_kernel_status": (C.c_int, [C.POINTER(C.c_int), C.c_int]),

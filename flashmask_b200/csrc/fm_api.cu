@@ -99,6 +99,7 @@ int fill_kparams(const fm_attn_args* a, AttnKParams* p, bool backward) {
   p->md.nblk_pad = fm_mask_nblk_pad(a->Sk, a->tile_n > 0 ? a->tile_n : 64);
   p->md.BHm = p->md.mask_B * p->md.Hm;
   p->md.Sq = a->Sq; p->md.Sk = a->Sk;
+  if (a->ncols) { p->fwd_order = a->fwd_order; p->dq_order = a->dq_order; p->dkdv_order = a->dkdv_order; }
   if (backward) {
     p->d_o = a->d_o; p->dq = a->dq; p->dk = a->dk; p->dv = a->dv_out; p->dsink = a->dsink;
     p->do_b = a->do_stride[0]; p->do_s = a->do_stride[1]; p->do_h = a->do_stride[2];
@@ -168,6 +169,63 @@ extern "C" int fm_fwd(const fm_attn_args* a, void* stream) {
   FM_REQUIRE(!fwd_uses_sm100(a->d, a->dv), FM_ERR_INVALID_ARGUMENT,
              "fm_fwd: q/k/v must be 16-byte aligned");
   return fwd_mma_launch(p, a->dtype, (cudaStream_t)stream);
+}
+
+// Geometry of a launch order: the ordered axis, rows per unit, the block the work is
+// counted in, and how often a unit repeats (heads per mask head, batches per mask batch).
+// Only the tcgen05 variants read an order.
+struct OrderGeom { int axis, block_rows, n_units, n_other, heads, rep_h, rep_b; int64_t E, n_cta; };
+static bool order_geometry(const fm_attn_args* a, int which, OrderGeom* g) {
+  if (!a || a->ncols == 0 || a->Sq <= 0 || a->Sk <= 0 || a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0) return false;
+  if (!(a->Hm == 1 || a->Hm == a->Hkv) || !(a->mask_B == 1 || a->mask_B == a->B) || a->Hq % a->Hkv) return false;
+  const int nk = (a->Sk + 127) / 128;
+  if (which == FM_ORDER_FWD) {
+    if (!fwd_uses_sm100(a->d, a->dv)) return false;
+    *g = OrderGeom{0, 256, (a->Sq + 255) / 256, nk, a->Hq};
+  } else if (which == FM_ORDER_BWD_DQ) {
+    if (!bwd_uses_sm100(a->d, a->dv)) return false;
+    *g = OrderGeom{0, 128, (a->Sq + 127) / 128, nk, a->Hq};
+  } else if (which == FM_ORDER_BWD_DKDV) {
+    if (!bwd_uses_sm100(a->d, a->dv)) return false;
+    *g = OrderGeom{1, 64, nk, (a->Sq + 63) / 64, a->Hkv};
+  } else {
+    return false;
+  }
+  g->rep_h = g->heads / a->Hm;
+  g->rep_b = a->B / a->mask_B;
+  g->E = (int64_t)a->mask_B * a->Hm * g->n_units;
+  g->n_cta = g->E * g->rep_h * g->rep_b;
+  if (g->E > FM_ORDER_MAX_UNITS || g->n_cta >= (1ll << 30)) return false;
+  // Where an order pays (measured): reading the table costs every CTA one dependent global
+  // load before it can start.  The forward's 256-row CTAs differ most in work and always gain;
+  // the dK/dV kernel gains while its launch is a few waves of long CTAs (each loops over the q
+  // heads of its group) and loses on many short ones; the dQ kernel's 128-row CTAs balance well
+  // enough in index order.  FLASHMASK_B200_ORDER_FORCE=1 builds every order (tests, A/B runs).
+  const char* force = getenv("FLASHMASK_B200_ORDER_FORCE");
+  if (force && strcmp(force, "1") == 0) return true;
+  if (which == FM_ORDER_FWD) return true;
+  if (which == FM_ORDER_BWD_DKDV) return g->n_cta <= 8 * 148;
+  return false;
+}
+
+extern "C" int64_t fm_launch_order_ints(const fm_attn_args* a, int which) {
+  OrderGeom g;
+  if (!order_geometry(a, which, &g)) return 0;
+  return 2 * g.n_cta + 2 * g.E;
+}
+
+extern "C" int fm_launch_order(const fm_attn_args* a, int which, int32_t* out, void* stream) {
+  OrderGeom g;
+  FM_REQUIRE(a && out, FM_ERR_INVALID_ARGUMENT, "fm_launch_order: NULL argument");
+  FM_REQUIRE(order_geometry(a, which, &g), FM_ERR_UNSUPPORTED,
+             "fm_launch_order: no order for this kernel variant / mask (fm_launch_order_ints returned 0)");
+  FM_REQUIRE(a->minmax && a->tile_n == 128, FM_ERR_INVALID_ARGUMENT,
+             "fm_launch_order: minmax must be prepared with tile_n = 128");
+  FM_REQUIRE(((uintptr_t)out & 7) == 0, FM_ERR_INVALID_ARGUMENT, "fm_launch_order: out must be 8-byte aligned");
+  MaskDesc md{a->mask, a->minmax, a->ncols, a->causal, a->Hm, a->mask_B, fm_mask_nblk_pad(a->Sk, 128),
+              a->mask_B * a->Hm, a->Sq, a->Sk};
+  return launch_order_build(md, g.axis, g.block_rows, 128, g.n_units, g.n_other, g.rep_h, g.rep_b, g.heads, out,
+                            (cudaStream_t)stream);
 }
 
 extern "C" size_t fm_bwd_workspace_bytes(const fm_attn_args* a) {

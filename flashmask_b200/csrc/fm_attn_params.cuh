@@ -17,8 +17,24 @@ struct AttnKParams {
   int Sq_r;  // Sq rounded up to the row tile, stride of the per-row workspaces
   float scale, scale_log2;
   MaskDesc md;
+  // optional longest-work-first launch orders (unit ids over (mask_b, mask_h, unit)); nullptr = index order
+  const int32_t* fwd_order; const int32_t* dq_order; const int32_t* dkdv_order;
 };
 
-int fill_kparams(const fm_attn_args* a, AttnKParams* p, bool backward);
+// CTA coordinates under a launch order: the CTAs of a launch are numbered in
+// dispatch order L = x + gx*(y + gy*z) and table[L] = (unit, b * heads + head).
+struct OrderedCta { int b, head, unit; };
+__device__ __forceinline__ OrderedCta ordered_cta(const int32_t* table, int heads) {
+  const unsigned L = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  const int2 e = __ldg(reinterpret_cast<const int2*>(table) + L);
+  OrderedCta c;
+  c.unit = e.x; c.head = e.y % heads; c.b = e.y / heads;
+  return c;
+}
+
+// Units a launch table may cover (one CTA builds it, the unit work staged in shared memory).
+constexpr int FM_ORDER_MAX_UNITS = 4096;
+int launch_order_build(const MaskDesc& md, int axis, int block_rows, int tile_n, int n_units, int n_other,
+                       int rep_h, int rep_b, int heads, int32_t* out, cudaStream_t s);
 
 }  // namespace fm

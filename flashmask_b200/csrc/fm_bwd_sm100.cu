@@ -104,9 +104,17 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
   int b, hk, hq0, row0;  // row0: first key (DKDV) or first query (DQ) of the stationary tile
   if (MODE == MODE_DKDV) {
     b = blockIdx.z; hk = blockIdx.y; hq0 = hk * G; row0 = blockIdx.x * 128;
+    if (p.dkdv_order) {
+      const OrderedCta c = ordered_cta(p.dkdv_order, p.Hkv);
+      b = c.b; hk = c.head; hq0 = hk * G; row0 = c.unit * 128;
+    }
   } else {
     const int n_tiles = (p.Sq + 127) / 128;
     b = blockIdx.z; hq0 = blockIdx.y; hk = hq0 / G; row0 = (n_tiles - 1 - (int)blockIdx.x) * 128;
+    if (p.dq_order) {
+      const OrderedCta c = ordered_cta(p.dq_order, p.Hq);
+      b = c.b; hq0 = c.head; hk = hq0 / G; row0 = c.unit * 128;
+    }
   }
   const int bh_mask = md.ncols ? ((md.mask_B == 1 ? 0 : b) * md.Hm + hq0 / (p.Hq / md.Hm)) : 0;
   const int n_heads = (MODE == MODE_DKDV) ? G : 1;

@@ -71,8 +71,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
   const int lane = tid & 31;
   const int n_tiles = (p.Sq + 255) / 256;
-  const int t = n_tiles - 1 - blockIdx.x;
-  const int hq = blockIdx.y, b = blockIdx.z;
+  int t = n_tiles - 1 - blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
+  if (p.fwd_order) {
+    const OrderedCta c = ordered_cta(p.fwd_order, p.Hq);
+    t = c.unit; hq = c.head; b = c.b;
+  }
   const int hk = hq / (p.Hq / p.Hkv);
   const MaskDesc& md = p.md;
   const int bh_mask = md.ncols ? ((md.mask_B == 1 ? 0 : b) * md.Hm + hq / (p.Hq / md.Hm)) : 0;

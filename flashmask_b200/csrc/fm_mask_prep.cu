@@ -2,7 +2,7 @@
 // then (Q tile, K tile) classification + surviving-tile counts, and the exact
 // unmasked-pair count used as the work measure.  Integer, HBM-bound work:
 // coalesced vector loads, one warp per K tile / per Q tile.
-#include "fm_common.cuh"
+#include "fm_attn_params.cuh"
 
 namespace fm {
 
@@ -95,9 +95,107 @@ __global__ void __launch_bounds__(256) count_visible_kernel(MaskDesc md, int64_t
   }
 }
 
+// Longest-work-first launch table of one kernel, built by ONE CTA of 1024 threads.
+//   1. work of every unit (axis 0: a block of `block_rows` query rows -> K tiles it keeps;
+//      axis 1: a K tile -> `block_rows`-row query blocks it keeps), one warp per unit;
+//   2. units are dealt into FM_ORDER_BUCKETS work classes relative to the heaviest unit and
+//      ordered by (class, index): heaviest class first, index order inside a class;
+//   3. the launch table lists, class by class, every repeat (heads sharing the mask head,
+//      batches sharing a broadcast mask) of the class's units, repeat-major: CTAs next to
+//      each other in dispatch order work on neighbouring tiles of the same head, as in the
+//      index order, so operands shared between neighbouring tiles still meet in L2.
+// smem: work[E], order[E], hist/start[FM_ORDER_BUCKETS + 1], red[32], class[E] bytes.
+constexpr int FM_ORDER_BUCKETS = 8;
+
+__global__ void __launch_bounds__(1024) launch_order_kernel(MaskDesc md, int axis, int block_rows, int tile_n,
+                                                            int n_units, int n_other, int rep_h, int rep_b,
+                                                            int heads, int32_t* __restrict__ out) {
+  extern __shared__ int32_t sm[];
+  const int E = md.BHm * n_units;
+  int32_t* swork = sm;
+  int32_t* sorder = sm + E;
+  int32_t* sstart = sm + 2 * E;           // [FM_ORDER_BUCKETS + 1]
+  int32_t* sred = sstart + FM_ORDER_BUCKETS + 1;  // [32]
+  uint8_t* sclass = reinterpret_cast<uint8_t*>(sred + 32);  // [E]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int n_cta = E * rep_h * rep_b;
+  int2* table = reinterpret_cast<int2*>(out);
+  int32_t* gwork = out + 2 * (size_t)n_cta;
+  int32_t* gorder = gwork + E;
+
+  for (int e = warp; e < E; e += 32) {
+    const int bh = e / n_units, u = e % n_units;
+    int cnt = 0;
+    if (axis == 0) {
+      const int ms = u * block_rows, me = min(ms + block_rows, md.Sq);
+      for (int n = lane; n < n_other; n += 32) cnt += tile_flags(md, bh, n, ms, me, tile_n) != 0;
+    } else {
+      for (int t = lane; t < n_other; t += 32) {
+        const int ms = t * block_rows, me = min(ms + block_rows, md.Sq);
+        cnt += tile_flags(md, bh, u, ms, me, tile_n) != 0;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+    if (lane == 0) { swork[e] = cnt; gwork[e] = cnt; }
+  }
+  if (tid <= FM_ORDER_BUCKETS) sstart[tid] = 0;
+  __syncthreads();
+
+  int mx = 0;
+  for (int e = tid; e < E; e += 1024) mx = max(mx, swork[e]);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) sred[warp] = mx;
+  __syncthreads();
+  mx = 0;
+  for (int w = 0; w < 32; ++w) mx = max(mx, sred[w]);
+  for (int e = tid; e < E; e += 1024) {
+    const int k = (int)(((long long)(mx - swork[e]) * FM_ORDER_BUCKETS) / (mx + 1));  // 0 = heaviest class
+    sclass[e] = (uint8_t)k;
+    atomicAdd(&sstart[k + 1], 1);
+  }
+  __syncthreads();
+  if (tid == 0)
+    for (int k = 0; k < FM_ORDER_BUCKETS; ++k) sstart[k + 1] += sstart[k];
+  __syncthreads();
+  for (int e = tid; e < E; e += 1024) {
+    const int k = sclass[e];
+    int before = 0;
+    for (int j = 0; j < e; ++j) before += sclass[j] == k;
+    const int r = sstart[k] + before;
+    sorder[r] = e;
+    gorder[r] = e;
+  }
+  __syncthreads();
+
+  const int rep = rep_h * rep_b;
+  for (int L = tid; L < n_cta; L += 1024) {
+    int k = 0;
+    while (L >= rep * sstart[k + 1]) ++k;
+    const int size = sstart[k + 1] - sstart[k];
+    const int l = L - rep * sstart[k];
+    const int rr = l / size;
+    const int id = sorder[sstart[k] + l % size];
+    const int unit = id % n_units;
+    const int head = (id / n_units) % md.Hm * rep_h + rr % rep_h;
+    const int b = md.mask_B == 1 ? rr / rep_h : id / (n_units * md.Hm);
+    table[L] = make_int2(unit, b * heads + head);
+  }
+}
+
 }  // namespace fm
 
 using namespace fm;
+
+int fm::launch_order_build(const MaskDesc& md, int axis, int block_rows, int tile_n, int n_units, int n_other,
+                           int rep_h, int rep_b, int heads, int32_t* out, cudaStream_t s) {
+  const int E = md.BHm * n_units;
+  const size_t smem = sizeof(int32_t) * (2 * (size_t)E + FM_ORDER_BUCKETS + 1 + 32) + (size_t)E;
+  launch_order_kernel<<<1, 1024, smem, s>>>(md, axis, block_rows, tile_n, n_units, n_other, rep_h, rep_b, heads, out);
+  FM_CUDA_TRY(cudaGetLastError());
+  return FM_OK;
+}
 
 extern "C" int fm_mask_nblk_pad(int Sk, int tile_n) {
   if (tile_n <= 0) return 0;

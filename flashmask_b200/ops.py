@@ -10,8 +10,9 @@ from __future__ import annotations
 
 import ctypes as C
 import math
-from dataclasses import dataclass
-from typing import Optional, Tuple
+import os
+from dataclasses import dataclass, field
+from typing import Dict, Optional, Tuple
 
 import torch
 
@@ -56,6 +57,8 @@ class FlashMaskInfo:
     minmax: torch.Tensor                        # [8, B*Hm, nblk_pad] int32
     valid_block_count: Optional[torch.Tensor]   # [B, Hm, Tq] int32
     tile_class: Optional[torch.Tensor]          # [B, Hm, Tq, Tk] int8
+    # longest-work-first launch tables, built on first use: (which, d, dv, Sq, B, Hq, Hkv) -> int32 tensor or None
+    orders: Dict[tuple, Optional[torch.Tensor]] = field(default_factory=dict)
 
 
 def prepare_mask(idx: torch.Tensor, Sq: int, causal: bool, tile_m: int, tile_n: int,
@@ -76,6 +79,27 @@ def prepare_mask(idx: torch.Tensor, Sq: int, causal: bool, tile_m: int, tile_n: 
                                    cls.data_ptr() if want_class else None, _stream(idx)),
                "fm_mask_prepare")
     return FlashMaskInfo(idx, causal, tile_m, tile_n, minmax, cnt, cls)
+
+
+def _launch_order(a: "_lib.AttnArgs", info: FlashMaskInfo, which: int, ref: torch.Tensor) -> Optional[int]:
+    """Device pointer of the launch order ``which`` (FM_ORDER_*) for this mask and kernel
+    variant, or None when the variant takes none.  Built once per FlashMaskInfo
+    (one small kernel on the current stream).  FLASHMASK_B200_ORDER=0 turns all orders off,
+    a comma list out of fwd,dq,dkdv keeps only those (A/B runs)."""
+    sel = os.environ.get("FLASHMASK_B200_ORDER", "1")
+    if sel != "1" and ("fwd", "dq", "dkdv")[which] not in sel.split(","):
+        return None
+    key = (which, a.d, a.dv, a.Sq, a.B, a.Hq, a.Hkv)
+    if key not in info.orders:
+        lib = _lib.load()
+        n = lib.fm_launch_order_ints(C.byref(a), which)
+        buf = None
+        if n:
+            buf = torch.empty(n, dtype=torch.int32, device=ref.device)
+            _lib.check(lib.fm_launch_order(C.byref(a), which, buf.data_ptr(), _stream(ref)), "fm_launch_order")
+        info.orders[key] = buf
+    buf = info.orders[key]
+    return None if buf is None else buf.data_ptr()
 
 
 def count_visible(idx: torch.Tensor, Sq: int, causal: bool) -> torch.Tensor:
@@ -177,6 +201,8 @@ def _flash_attn_fwd(q, k, v, startend_row_indices=None, softmax_scale=None, caus
     lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device)
     sink32 = _sink_fp32(learnable_sink, Hq, q.device)
     a = _base_args(q, k, v, out, lse, idx, info, causal, softmax_scale, sink32)
+    if info is not None:
+        a.fwd_order = _launch_order(a, info, _lib.FM_ORDER_FWD, q)
     _lib.check(_lib.load().fm_fwd(C.byref(a), _stream(q)), "fm_fwd")
     return out, lse
 
@@ -212,6 +238,9 @@ def _flash_attn_bwd(q, k, v, out, dout, lse, startend_row_indices=None, softmax_
     if dsink32 is not None:
         a.dsink = dsink32.data_ptr()
     lib = _lib.load()
+    if info is not None:
+        a.dq_order = _launch_order(a, info, _lib.FM_ORDER_BWD_DQ, q)
+        a.dkdv_order = _launch_order(a, info, _lib.FM_ORDER_BWD_DKDV, q)
     nbytes = lib.fm_bwd_workspace_bytes(C.byref(a))
     ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=q.device)
     a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes

@@ -135,6 +135,10 @@ typedef struct fm_attn_args {
   int64_t dq_stride[3];
   int64_t dk_stride[3];
   int64_t dv_stride[3];
+  /* Optional launch orders from fm_launch_order (NULL: tiles in index order). */
+  const int32_t* fwd_order;  /* FM_ORDER_FWD, read by fm_fwd                     */
+  const int32_t* dq_order;   /* FM_ORDER_BWD_DQ, read by fm_bwd                  */
+  const int32_t* dkdv_order; /* FM_ORDER_BWD_DKDV, read by fm_bwd                */
 } fm_attn_args;
 
 /* Tile shape (rows of Q, columns of K per tile) the forward / backward kernel
@@ -150,6 +154,44 @@ FM_API int fm_bwd_tile_shape(int d, int dv, int* tile_m, int* tile_n);
  * FlashAttentionForwardSm100 (flashmask/cute/flash_fwd_sm100.py:1485-2104).
  * Uses no workspace. */
 FM_API int fm_fwd(const fm_attn_args* args, void* stream);
+
+/*
+ * Longest-work-first launch order for sparse masks.  A kernel's CTAs are handed
+ * to the SMs in launch order, so starting the heaviest tiles first keeps the
+ * tail of the launch short when tiles differ widely in the number of K tiles
+ * (or query tiles) the mask leaves them.  `which` selects the kernel:
+ * FM_ORDER_FWD (units of 256 query rows), FM_ORDER_BWD_DQ (128 query rows),
+ * FM_ORDER_BWD_DKDV (one 128-column K tile; work = 64-row query blocks kept).
+ * Units are dealt into 8 work classes relative to the heaviest unit; the launch
+ * runs class by class, heaviest first, and inside a class head by head with
+ * the units in index order, so neighbouring CTAs still share operands in L2.
+ * Only the problem geometry of `args` is read (B, Hq, Hkv, mask_B, Hm, Sq, Sk,
+ * ncols, causal, d, dv, minmax, tile_n).  With E = mask_B*Hm*units and
+ * N = E * (heads/Hm) * (B/mask_B) = the number of CTAs of the kernel:
+ *   fm_launch_order_ints  number of int32 `out` must hold, 2*N + 2*E, or 0
+ *                         when the kernel variant for (d, dv) takes no order,
+ *                         there is no mask tensor, E > 4096, or an order is not
+ *                         expected to pay: every CTA reads its table entry before
+ *                         it can start, so the forward is always ordered, the
+ *                         dK/dV kernel while N <= 8 waves of the 148 SMs, the dQ
+ *                         kernel never (FLASHMASK_B200_ORDER_FORCE=1 in the
+ *                         environment builds all three).
+ *   fm_launch_order       out[2L], out[2L+1] = (unit, b*heads + head) of the
+ *                         L-th CTA in dispatch order; then E ints of work per
+ *                         unit (mask_b, mask_h, unit flattened) and E ints of
+ *                         the units by (class, index).  `out` is 8-byte
+ *                         aligned.  Pass it as the matching *_order field of
+ *                         later fm_fwd / fm_bwd calls with the same mask and
+ *                         the same B, Hq, Hkv.
+ * Plays the role of the reference's longest-processing-time tile schedulers
+ * (flashmask/cute/tile_scheduler.py:400-539, 542-660), which order by causal
+ * geometry only; here the order follows the mask itself.
+ */
+#define FM_ORDER_FWD 0
+#define FM_ORDER_BWD_DQ 1
+#define FM_ORDER_BWD_DKDV 2
+FM_API int64_t fm_launch_order_ints(const fm_attn_args* args, int which);
+FM_API int fm_launch_order(const fm_attn_args* args, int which, int32_t* out, void* stream);
 
 /* Device-side status of the kernels that wait on barriers (the tcgen05
  * variants): every wait is bounded, and a wait that ran out makes its CTA

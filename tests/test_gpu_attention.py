@@ -190,6 +190,28 @@ def test_deterministic_bitwise(fwd_variant):
             assert torch.equal(a[n], b[n]), n
 
 
+@pytest.mark.parametrize("kind,mask_b,hm", [("causal_doc", 2, 1), ("four_column", 1, 2), ("share_question", 2, 2),
+                                            ("bidir_doc", 1, 1)])
+def test_launch_order_changes_no_bit(kind, mask_b, hm, monkeypatch):
+    """The longest-work-first launch order only permutes which CTA runs which tile:
+    results are bitwise those of the index order, for every mask batch / head broadcast."""
+    B, S, Hq, Hkv = 2, 1024, 8, 2
+    idx_np, causal = _mask(kind, B, S, S, 33)
+    idx_np = np.ascontiguousarray(idx_np[:mask_b]).copy()
+    if hm > 1:   # distinct masks per mask head
+        other = np.clip(idx_np + np.array(S // 7, dtype=np.int32), 0, S).astype(np.int32)
+        idx_np = np.concatenate([idx_np, other], axis=1)
+    q, k, v, do, s = make_inputs(B, S, S, Hq, Hkv, 128, 128, 33, sink=True)
+    idx = torch.from_numpy(idx_np).cuda()
+    monkeypatch.setenv("FLASHMASK_B200_ORDER_FORCE", "1")   # all three kernels, whatever the size
+    monkeypatch.setenv("FLASHMASK_B200_ORDER", "0")
+    a = run_product(q.cuda(), k.cuda(), v.cuda(), do.cuda(), idx, causal, s, deterministic=True)
+    monkeypatch.setenv("FLASHMASK_B200_ORDER", "1")
+    b = run_product(q.cuda(), k.cuda(), v.cuda(), do.cuda(), idx, causal, s, deterministic=True)
+    for n in ("out", "lse", "dq", "dk", "dv", "dsink"):
+        assert torch.equal(a[n], b[n]), n
+
+
 def test_layout_invariance(fwd_variant):
     """Contiguous vs permuted storage of q/k/v give bitwise equal results
     (reference: tests/torch/test_flashmask.py:354-396)."""

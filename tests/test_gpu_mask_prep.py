@@ -80,3 +80,70 @@ def test_full_size_properties():
     # every document diagonal tile is partial, far-away tiles are skipped
     assert (cls[:, :, np.arange(64), np.arange(64) * 2] == 1).all()
     assert (cls[:, :, 0, 2:] == 0).all()
+
+
+def _expected_launch_table(work, n_units, Hm, mask_B, rep_h, rep_b, heads, buckets=8):
+    """CPU restatement of the launch table: units in 8 work classes relative to the heaviest,
+    class by class, inside a class repeat-major (batch repeat, head repeat) with units in index order."""
+    mx = int(work.max()) if work.size else 0
+    klass = ((mx - work.astype(np.int64)) * buckets) // (mx + 1)
+    order = np.lexsort((np.arange(work.size), klass))
+    table = []
+    for k in range(buckets):
+        ids = order[klass[order] == k]
+        for rr in range(rep_h * rep_b):
+            for i in ids:
+                unit, hm, bm = i % n_units, (i // n_units) % Hm, i // (n_units * Hm)
+                b = rr // rep_h if mask_B == 1 else bm
+                table.append((unit, b * heads + hm * rep_h + rr % rep_h))
+    return order, np.array(table, dtype=np.int32).reshape(-1, 2)
+
+
+@pytest.mark.parametrize("Sq,Sk,mask_b,hm", [(4096, 4096, 2, 1), (1000, 1000, 1, 2), (384, 1333, 2, 2)])
+def test_launch_order_bit_exact(Sq, Sk, mask_b, hm, monkeypatch):
+    """fm_launch_order: work per unit equals the count of non-skipped tiles of the CPU
+    classification; the table is the CPU restatement's, every CTA exactly once."""
+    import ctypes as C
+    from flashmask_b200 import _lib
+    lib = _lib.load()
+    monkeypatch.setenv("FLASHMASK_B200_ORDER_FORCE", "1")   # also the orders the size policy would skip
+    B, Hq, Hkv = 2, 4, 2
+    for name, (idx_np, causal) in _masks(mask_b * hm, Sq, Sk, Sq + 3 * Sk):
+        idx_np = idx_np.copy()
+        idx_np[-1] = np.minimum(idx_np[-1] + (Sk // 5), Sq)
+        ncols = idx_np.shape[-1]
+        idx_np = np.ascontiguousarray(idx_np.reshape(mask_b, hm, Sk, ncols))
+        idx = torch.from_numpy(idx_np).cuda()
+        info = fm.prepare_mask(idx, Sq, causal, 128, 128)
+        mm = tiles.scan_max_min(idx_np, 128, causal)
+        a = _lib.AttnArgs()
+        a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.Hm, a.d, a.dv = B, Sq, Sk, Hq, Hkv, hm, 128, 128
+        a.ncols, a.causal, a.mask_B, a.tile_m, a.tile_n = ncols, int(causal), mask_b, 128, 128
+        a.mask, a.minmax = idx.data_ptr(), info.minmax.data_ptr()
+        for which, rows, axis, heads in ((_lib.FM_ORDER_FWD, 256, 3, Hq), (_lib.FM_ORDER_BWD_DQ, 128, 3, Hq),
+                                         (_lib.FM_ORDER_BWD_DKDV, 64, 2, Hkv)):
+            cls = tiles.classify_tiles(mm, mask_b, hm, Sq, Sk, ncols, causal, rows, 128)
+            work = (cls != 0).sum(axis=axis).reshape(-1)
+            n_units = work.size // (mask_b * hm)
+            rep_h, rep_b = heads // hm, B // mask_b
+            n_cta = work.size * rep_h * rep_b
+            n = lib.fm_launch_order_ints(C.byref(a), which)
+            assert n == 2 * n_cta + 2 * work.size, (name, which)
+            out = torch.full((n,), -1, dtype=torch.int32, device="cuda")
+            _lib.check(lib.fm_launch_order(C.byref(a), which, out.data_ptr(), None), "fm_launch_order")
+            out = out.cpu().numpy()
+            order, table = _expected_launch_table(work, n_units, hm, mask_b, rep_h, rep_b, heads)
+            assert np.array_equal(out[2 * n_cta:2 * n_cta + work.size], work), (name, which)
+            assert np.array_equal(out[2 * n_cta + work.size:], order), (name, which)
+            got = out[:2 * n_cta].reshape(-1, 2)
+            assert np.array_equal(got, table), (name, which)
+            assert len({(int(u), int(h)) for u, h in got}) == n_cta == n_units * heads * B
+    # no order where it does not pay, where the kernel variant takes none, or without a mask tensor
+    monkeypatch.delenv("FLASHMASK_B200_ORDER_FORCE")
+    assert lib.fm_launch_order_ints(C.byref(a), _lib.FM_ORDER_BWD_DQ) == 0
+    assert lib.fm_launch_order_ints(C.byref(a), _lib.FM_ORDER_FWD) > 0
+    a.d = a.dv = 64
+    assert lib.fm_launch_order_ints(C.byref(a), _lib.FM_ORDER_FWD) == 0
+    a.d = a.dv = 128
+    a.ncols = 0
+    assert lib.fm_launch_order_ints(C.byref(a), _lib.FM_ORDER_BWD_DKDV) == 0

@@ -54,7 +54,7 @@ def test_argument_errors_need_no_gpu():
 
 def test_struct_layout_matches_header():
     # 18 int32/float + 15 pointers/size_t + 24 int64
-    assert ctypes.sizeof(_lib.AttnArgs) == 18 * 4 + 15 * 8 + 24 * 8
+    assert ctypes.sizeof(_lib.AttnArgs) == 18 * 4 + 15 * 8 + 24 * 8 + 3 * 8
 
 
 def test_workload_shapes():
