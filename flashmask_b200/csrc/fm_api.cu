@@ -70,6 +70,7 @@ static int validate_common(const fm_attn_args* a, const char* who) {
              "%s: ncols must be 0, 1, 2 or 4", who);
   if (a->ncols) {
     FM_REQUIRE(a->mask && a->minmax, FM_ERR_INVALID_ARGUMENT, "%s: mask given but mask/minmax is NULL", who);
+    FM_REQUIRE(((uintptr_t)a->minmax & 15) == 0, FM_ERR_INVALID_ARGUMENT, "%s: minmax must be 16-byte aligned", who);
     FM_REQUIRE(a->Hm == 1 || a->Hm == a->Hkv, FM_ERR_INVALID_ARGUMENT,
                "%s: mask heads (%d) must be 1 or Hkv", who, a->Hm);
     FM_REQUIRE(a->mask_B == a->B || a->mask_B == 1, FM_ERR_INVALID_ARGUMENT,

@@ -41,11 +41,17 @@ __device__ __forceinline__ void trace_ev(int role, int& n, int ev, int k) {
     ++n;
   }
 }
+// Phase stamps of the CTAs (x < 64, y = 0, z = 0): one clock value per phase boundary.
+__device__ long long g_prof[2 * 64 * 16];   // [mode][cta][stamp]
 #define TRACE_DECL int trace_n = 0;
 #define TRACE(role, ev, k) trace_ev(role, trace_n, ev, k)
+#define PROF(slot) do { if (blockIdx.y == 0 && blockIdx.z == 0 && blockIdx.x < 64) g_prof[(MODE * 64 + blockIdx.x) * 16 + (slot)] = clock64(); } while (0)
+#define PROF_VAL(slot, v) do { if (blockIdx.y == 0 && blockIdx.z == 0 && blockIdx.x < 64) g_prof[(MODE * 64 + blockIdx.x) * 16 + (slot)] = (v); } while (0)
 #else
 #define TRACE_DECL
 #define TRACE(role, ev, k)
+#define PROF(slot)
+#define PROF_VAL(slot, v)
 #endif
 
 struct BwdSm100Cfg {
@@ -96,6 +102,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
   const int lane = tid & 31;
   TRACE_DECL
+  if (tid == 0) PROF(0);
+  // descriptor fetches start before anything else: the first loads wait on them
+  if (warp == 8 && lane == 0) {
+    tma_prefetch_desc(&tm_stat1); tma_prefetch_desc(&tm_stat2);
+    tma_prefetch_desc(&tm_str1); tma_prefetch_desc(&tm_str2);
+  }
   const MaskDesc& md = p.md;
   const int off = p.Sk - p.Sq;
   const int G = p.Hq / p.Hkv;
@@ -118,6 +130,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
   }
   const int bh_mask = md.ncols ? ((md.mask_B == 1 ? 0 : b) * md.Hm + hq0 / (p.Hq / md.Hm)) : 0;
   const int n_heads = (MODE == MODE_DKDV) ? G : 1;
+  if (tid == 0) PROF(15);
 
   if (tid == 0) misc[4] = 0;
   if (warp == 8 && lane == 0) {
@@ -138,24 +151,29 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
         tma_load_4d(sStat + Cfg::TILE_BYTES + dc * Cfg::SUB128, &tm_stat2, bar(Cfg::B_STAT), dc * 64, hs, row0, b);
       }
     }
-    tma_prefetch_desc(&tm_str1); tma_prefetch_desc(&tm_str2);
+    PROF(11);
   }
   if (warp == 9) {
+    if (lane == 0) PROF(14);
     tmem_alloc(sbase + Cfg::OFF_MISC, 512);
     tmem_relinquish();
+    if (lane == 0) PROF(12);
   }
   if (warp == 10) {
+    // the reductions the classification needs are staged in the (still idle) operand ring
+    int32_t* stage = reinterpret_cast<int32_t*>(smem + Cfg::OFF_RING);
     int cnt = 0;
     if (MODE == MODE_DKDV) {
       // 64-query half tiles that see key tile n = row0/128, ascending
       const int n = row0 / 128;
       const int n_half = (p.Sq + 63) / 64;
+      const MaskDesc ms = stage_minmax(md, bh_mask, n & ~3, n + 1, stage, 4, lane);
       int lo = 0;
       if (md.causal) lo = max(0, (row0 - off) / 64);
       for (int base = lo; base < n_half; base += 32) {
         const int idx = base + lane;
         uint32_t f = 0;
-        if (idx < n_half) f = tile_flags(md, bh_mask, n, idx * 64, min(idx * 64 + 64, p.Sq), 128);
+        if (idx < n_half) f = tile_flags(ms, 0, n, idx * 64, min(idx * 64 + 64, p.Sq), 128);
         const uint32_t bal = __ballot_sync(0xffffffffu, f != 0);
         const int pos = cnt + __popc(bal & ((1u << lane) - 1u));
         if (f && pos < Cfg::LIST_MAX) list[pos] = (uint32_t)idx | (f << 16);
@@ -167,11 +185,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
       const int n_half = (p.Sk + 63) / 64;
       int hi = n_half;
       if (md.causal) hi = max(0, min(n_half, (me + off + 63) / 64));
+      const MaskDesc ms = stage_minmax(md, bh_mask, 0, (hi + 1) >> 1, stage, Cfg::LIST_MAX, lane);
       for (int base = hi - 1; base >= 0; base -= 32) {
         const int idx = base - lane;
         uint32_t f = 0;
         if (idx >= 0) {
-          f = tile_flags(md, bh_mask, idx >> 1, row0, me, 128);
+          f = tile_flags(ms, 0, idx >> 1, row0, me, 128);
           if (md.causal && idx * 64 > me - 1 + off) f = 0;
         }
         const uint32_t bal = __ballot_sync(0xffffffffu, f != 0);
@@ -181,6 +200,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
       }
     }
     if (lane == 0) misc[1] = min(cnt, Cfg::LIST_MAX);
+    fence_proxy_async_smem();   // the staging area is handed back to the TMA loads of the ring
+    if (lane == 0) PROF(13);
   }
   tc_fence_before();
   __syncthreads();
@@ -188,6 +209,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
   const uint32_t tmem = (uint32_t)misc[0];
   const int cnt = misc[1];
   WaitCtx wc{misc + 4, global_timer_ns() + 2000000000ull};
+  if (tid == 0) { PROF(1); PROF_VAL(10, (long long)cnt * ((MODE == MODE_DKDV) ? p.Hq / p.Hkv : 1)); }
   if (cnt == 0) {
     // this tile's gradients are all zero: store them; the stationary loads already
     // in flight are awaited and the tensor memory is returned before leaving
@@ -259,6 +281,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
       ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_GFULL + pz), (uint32_t)(k >> 1) & 1u, wc));
       if (!ok) break;
       if (r == 0) TRACE(2 + pz, 12, k);   // scores observed ready
+      if (tid == 0 && k == 0) PROF(4);
       tc_fence_after();
       const uint8_t* aux = smem + Cfg::OFF_AUX + slot * Cfg::AUX_BYTES;
       const uint32_t NEG = 0xff800000u;
@@ -367,6 +390,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
     if (ok && K_items > 0) {
       ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_ACC), 0u, wc));
       tc_fence_after();
+      if (tid == 0) PROF(7);
     }
     if (ok) {
       if (MODE == MODE_DKDV) {
@@ -440,6 +464,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
                 *reinterpret_cast<const uint4*>(stage + rr * 256 + ((cc ^ (rr & 15)) << 4));
         }
       }
+      if (tid == 0) PROF(8);
     }
   } else {
     if (warp == 8) {
@@ -492,6 +517,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
         constexpr uint32_t idesc_g = make_idesc(IS_BF16, 128, 64, 0, 0);
         constexpr uint32_t idesc_acc = make_idesc(IS_BF16, 128, 128, 0, 1);
         bool ok = mbar_wait(bar(Cfg::B_STAT), 0u, wc);
+        PROF(2);
         // descriptors are built once; per MMA only a constant is added to the
         // 14-bit address field (all smem offsets are multiples of 16 bytes)
         const uint64_t dA1 = make_sdesc(sStat, 16, 1024);
@@ -523,7 +549,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
             tc_commit(bar(Cfg::B_GFULL + pz));
           }
         };
-        issue_g_early(0); if (ok) issue_g_late(0);
+        issue_g_early(0); PROF(3); if (ok) issue_g_late(0);
         if (K_items > 1 && ok) { issue_g_early(1); if (ok) issue_g_late(1); }
         for (int k = 0; k < K_items && ok; ++k) {
           const int slot = k % Cfg::NSLOT, pz = k & 1;
@@ -556,6 +582,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
           if (k + 2 < K_items) issue_g_late(k + 2);
         }
         if (ok) tc_commit(bar(Cfg::B_ACC));
+        PROF(6);
       }
       __syncwarp();
     }
@@ -565,6 +592,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (tid == 0) PROF(9);
   if (misc[4] != 0) {
     const uint64_t t_end = global_timer_ns() + 200000ull;
     while (global_timer_ns() < t_end) __nanosleep(1000);
@@ -623,6 +651,9 @@ extern "C" __attribute__((visibility("default"))) int fm_debug_trace_read(int* o
   static int zeros[4 * 3 * 2048];
   cudaMemcpyToSymbol(g_trace, zeros, sizeof(zeros));
   return 0;
+}
+extern "C" __attribute__((visibility("default"))) int fm_debug_prof_read(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_prof, sizeof(long long) * 2 * 64 * 16);
 }
 #endif
 

@@ -114,6 +114,40 @@ __device__ __forceinline__ uint32_t tile_flags(const MaskDesc& md, int bh_mask, 
   return flags;
 }
 
+// One warp copies the per-K-tile reductions of tiles [n_lo, n_hi) of mask row `bh` into
+// shared memory with all its global loads in flight at once, and returns a descriptor
+// whose tile_flags(staged, 0, n, ...) reads them from there.  Walking a tile list with
+// tile_flags on the global copy costs one dependent global round trip per 32 tiles; this
+// way the whole range costs one.  n_lo is a multiple of 4 (16-byte loads; every row of
+// `minmax` is padded to a multiple of 4 tiles and 16-byte aligned), `stage` holds
+// 8 * cap ints with cap a multiple of 4 and >= n_hi - n_lo.
+__device__ __forceinline__ MaskDesc stage_minmax(const MaskDesc& md, int bh, int n_lo, int n_hi,
+                                                 int32_t* stage, int cap, int lane) {
+  MaskDesc s = md;
+  if (!md.ncols) return s;
+  const size_t slot = (size_t)md.BHm * md.nblk_pad;
+  const int32_t* src = md.minmax + (size_t)bh * md.nblk_pad + n_lo;
+  const int n4 = (n_hi - n_lo + 3) >> 2;
+  // reductions the mask carries: LTS always, LTE for causal 2-column and 4-column masks,
+  // UTS for 4-column, UTE for non-causal 2-column and 4-column
+  const uint32_t which = md.ncols == 1 ? 0x03u : (md.ncols == 4 ? 0xFFu : (md.causal ? 0x0Fu : 0xC3u));
+  for (int base = 0; base < n4; base += 32) {
+    const int i = base + lane;
+    int4 v[8];
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+      if ((which >> w & 1u) && i < n4) v[w] = __ldg(reinterpret_cast<const int4*>(src + w * slot) + i);
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+      if ((which >> w & 1u) && i < n4) reinterpret_cast<int4*>(stage + w * cap)[i] = v[w];
+  }
+  __syncwarp();
+  s.minmax = stage - n_lo;
+  s.BHm = 1;
+  s.nblk_pad = cap;
+  return s;
+}
+
 // Three-way class of the same tile: skipped / partial (needs an element mask) / unmasked.
 __device__ __forceinline__ int classify_tile(const MaskDesc& md, int bh_mask, int n, int ms, int me,
                                              int tile_n) {

@@ -70,6 +70,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int tid = threadIdx.x;
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
   const int lane = tid & 31;
+  // descriptor fetches start before anything else: the first loads wait on them
+  if (warp == 8 && lane == 0) { tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); }
   const int n_tiles = (p.Sq + 255) / 256;
   int t = n_tiles - 1 - blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
   if (p.fwd_order) {
@@ -99,7 +101,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         tma_load_4d(sQ + s * Cfg::Q_BYTES + dc * Cfg::SUB, &tm_q, bar(Cfg::B_QFULL + s), dc * 64, hq,
                     ms + 128 * s, b);
     }
-    tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
   }
   if (warp == 9) {
     tmem_alloc(sbase + Cfg::OFF_MISC, 512);
@@ -112,12 +113,15 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     int n_hi = nb;
     if (md.causal) n_hi = max(0, min(nb, (me_tile + off + 127) / 128));
     int cnt = 0, c0 = 0, c1 = 0;
+    // the reductions the classification needs are staged in the (still idle) K/V ring
+    const MaskDesc mst = stage_minmax(md, bh_mask, 0, n_hi, reinterpret_cast<int32_t*>(smem + Cfg::OFF_KV),
+                                      Cfg::LIST_MAX, lane);
     for (int base = n_hi - 1; base >= 0; base -= 32) {
       const int n = base - lane;
       uint32_t f0 = 0, f1 = 0;
       if (n >= 0) {
-        f0 = tile_flags(md, bh_mask, n, ms, min(ms + 128, p.Sq), 128);
-        if (ms + 128 < p.Sq) f1 = tile_flags(md, bh_mask, n, ms + 128, min(ms + 256, p.Sq), 128);
+        f0 = tile_flags(mst, 0, n, ms, min(ms + 128, p.Sq), 128);
+        if (ms + 128 < p.Sq) f1 = tile_flags(mst, 0, n, ms + 128, min(ms + 256, p.Sq), 128);
       }
       const bool keep = (f0 | f1) != 0;
       const uint32_t bal = __ballot_sync(0xffffffffu, keep);
@@ -128,6 +132,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       c1 += __popc(__ballot_sync(0xffffffffu, f1 != 0));
     }
     if (lane == 0) { misc[1] = min(cnt, Cfg::LIST_MAX); misc[2] = c0; misc[3] = c1; }
+    fence_proxy_async_smem();   // the staging area is handed back to the TMA loads of the ring
   }
   tc_fence_before();
   __syncthreads();
