@@ -19,6 +19,10 @@ struct AttnKParams {
   MaskDesc md;
   // optional longest-work-first launch orders (unit ids over (mask_b, mask_h, unit)); nullptr = index order
   const int32_t* fwd_order; const int32_t* dq_order; const int32_t* dkdv_order;
+  // state behind a backward table: [0] next table entry, [1] CTAs that left, [2] 1 when the persistent
+  // variant runs on this table, 0 when the one-unit-per-CTA variant does (written by the table builder)
+  int* dq_sched; int* dkdv_sched;
+  int dq_ncta, dkdv_ncta;   // entries of the tables
 };
 
 // CTA coordinates under a launch order: the CTAs of a launch are numbered in
@@ -35,6 +39,6 @@ __device__ __forceinline__ OrderedCta ordered_cta(const int32_t* table, int head
 // Units a launch table may cover (one CTA builds it, the unit work staged in shared memory).
 constexpr int FM_ORDER_MAX_UNITS = 4096;
 int launch_order_build(const MaskDesc& md, int axis, int block_rows, int tile_n, int n_units, int n_other,
-                       int rep_h, int rep_b, int heads, int32_t* out, cudaStream_t s);
+                       int rep_h, int rep_b, int heads, int item_mult, int32_t* out, cudaStream_t s);
 
 }  // namespace fm

@@ -116,17 +116,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
   int b, hk, hq0, row0;  // row0: first key (DKDV) or first query (DQ) of the stationary tile
   if (MODE == MODE_DKDV) {
     b = blockIdx.z; hk = blockIdx.y; hq0 = hk * G; row0 = blockIdx.x * 128;
-    if (p.dkdv_order) {
-      const OrderedCta c = ordered_cta(p.dkdv_order, p.Hkv);
-      b = c.b; hk = c.head; hq0 = hk * G; row0 = c.unit * 128;
-    }
   } else {
     const int n_tiles = (p.Sq + 127) / 128;
     b = blockIdx.z; hq0 = blockIdx.y; hk = hq0 / G; row0 = (n_tiles - 1 - (int)blockIdx.x) * 128;
-    if (p.dq_order) {
-      const OrderedCta c = ordered_cta(p.dq_order, p.Hq);
-      b = c.b; hq0 = c.head; hk = hq0 / G; row0 = c.unit * 128;
-    }
   }
   const int bh_mask = md.ncols ? ((md.mask_B == 1 ? 0 : b) * md.Hm + hq0 / (p.Hq / md.Hm)) : 0;
   const int n_heads = (MODE == MODE_DKDV) ? G : 1;
@@ -297,89 +289,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
       const uint32_t tT = (MODE == MODE_DKDV)
                               ? tG2
                               : tmem + lane_field + C_T + 32u * (uint32_t)((((k >> 1) & 1) << 1) + pz);
-#pragma unroll
-      for (int hc = 0; hc < 2; ++hc) {
-        uint32_t pk1[16], pk2[16];
-        if (MODE == MODE_DKDV) {
-          // columns are queries i0 + c; this lane is key j
-          const int i0 = idx * 64 + 32 * hc;
-          if (flags & ~FM_TF_ACTIVE) {
-            const int a0 = lts - i0, a1 = lte - i0, b0 = uts - i0, b1 = ute - i0;
-            const int cz = md.causal ? (row0 + r - off - i0) : INT_MIN;   // masked while c < cz
-#pragma unroll
-            for (int c = 0; c < 32; ++c)
-              if ((c >= a0 && c < a1) || (c >= b0 && c < b1) || c < cz) sr[hc][c] = NEG;
-          }
-          const float4* st = reinterpret_cast<const float4*>(aux) + 8 * hc;
-#pragma unroll
-          for (int c4 = 0; c4 < 8; ++c4) {
-            const float4 l4 = st[c4], d4 = st[16 + c4];
-            const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv4[4] = {d4.x, d4.y, d4.z, d4.w};
-            float pe[4], de[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              pe[u] = fast_exp2(fmaf(__uint_as_float(sr[hc][4 * c4 + u]), scale_log2, -lv[u]));
-              de[u] = pe[u] * (__uint_as_float(dr[hc][4 * c4 + u]) - dv4[u]);
-            }
-            pk1[2 * c4] = pack2<IS_BF16>(pe[0], pe[1]); pk1[2 * c4 + 1] = pack2<IS_BF16>(pe[2], pe[3]);
-            pk2[2 * c4] = pack2<IS_BF16>(de[0], de[1]); pk2[2 * c4 + 1] = pack2<IS_BF16>(de[2], de[3]);
-          }
-          tmem_st16(tT + 16 * hc, pk1);
-          tmem_st16(tT + 32 + 16 * hc, pk2);
-        } else {
-          // columns are keys jh0 + c; this lane is query i
-          const int jh0 = idx * 64 + 32 * hc;
-          const int i = row0 + r;
-          if (flags & FM_TF_BOUNDS) {
-            const int4* bp = reinterpret_cast<const int4*>(aux) + (8 * md.ncols) * hc;
-            if (md.ncols == 1) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const int4 v = bp[j];
-                if (i >= v.x) sr[hc][4 * j] = NEG;
-                if (i >= v.y) sr[hc][4 * j + 1] = NEG;
-                if (i >= v.z) sr[hc][4 * j + 2] = NEG;
-                if (i >= v.w) sr[hc][4 * j + 3] = NEG;
-              }
-            } else if (md.ncols == 2 && md.causal) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int4 v = bp[j];
-                if (i >= v.x && i < v.y) sr[hc][2 * j] = NEG;
-                if (i >= v.z && i < v.w) sr[hc][2 * j + 1] = NEG;
-              }
-            } else if (md.ncols == 2) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int4 v = bp[j];
-                if (i >= v.x || i < v.y) sr[hc][2 * j] = NEG;
-                if (i >= v.z || i < v.w) sr[hc][2 * j + 1] = NEG;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const int4 v = bp[j];
-                if ((i >= v.x && i < v.y) || (i >= v.z && i < v.w)) sr[hc][j] = NEG;
-              }
-            }
-          }
-          if (flags & (FM_TF_CAUSAL | FM_TF_RAGGED)) {
-            int jmax = p.Sk - 1 - jh0;
-            if (md.causal) jmax = min(jmax, i + off - jh0);
-#pragma unroll
-            for (int c = 0; c < 32; ++c)
-              if (c > jmax) sr[hc][c] = NEG;
-          }
-#pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[hc][2 * c]), scale_log2, -lse2_row));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[hc][2 * c + 1]), scale_log2, -lse2_row));
-            pk2[c] = pack2<IS_BF16>(p0 * (__uint_as_float(dr[hc][2 * c]) - dps_row),
-                                    p1 * (__uint_as_float(dr[hc][2 * c + 1]) - dps_row));
-          }
-          tmem_st16(tT + 16 * hc, pk2);
-        }
-      }
+#include "fm_bwd_sm100_item.inc"
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -505,8 +415,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
             int* dst = reinterpret_cast<int*>(smem + Cfg::OFF_AUX + slot * Cfg::AUX_BYTES);
             const int jh0 = idx * 64;
             const int32_t* src = md.mask + ((size_t)bh_mask * p.Sk + jh0) * md.ncols;
-            const int valid = min(64, p.Sk - jh0) * md.ncols;
-            for (int x = lane; x < 64 * md.ncols; x += 32) dst[x] = x < valid ? __ldg(src + x) : 0;
+            stage_bounds(dst, src, 64, min(64, p.Sk - jh0), md.ncols, lane);
           }
           mbar_arrive(bar(Cfg::B_RFULL + slot));
         }

@@ -148,6 +148,35 @@ __device__ __forceinline__ MaskDesc stage_minmax(const MaskDesc& md, int bh, int
   return s;
 }
 
+// One warp copies the row bounds of `cols` key columns (cols * ncols ints; cols is 64 or 128)
+// into shared memory, zero past `valid_cols` (a ragged last tile).  Every load is issued before
+// the first store, so the copy costs one global round trip however many bounds a column has.
+__device__ __forceinline__ void stage_bounds(int* dst, const int32_t* src, int cols, int valid_cols, int ncols,
+                                             int lane) {
+  const int n = cols * ncols;
+  if (valid_cols == cols && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+    const int n4 = n >> 2;                      // <= 128 vectors: at most 4 per lane
+    int4 v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (lane + 32 * i < n4) v[i] = __ldg(reinterpret_cast<const int4*>(src) + lane + 32 * i);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (lane + 32 * i < n4) reinterpret_cast<int4*>(dst)[lane + 32 * i] = v[i];
+  } else {
+    const int valid = valid_cols * ncols;
+    int v[16];                                  // <= 512 ints: at most 16 per lane
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int x = lane + 32 * i;
+      v[i] = (x < valid) ? __ldg(src + x) : 0;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (lane + 32 * i < n) dst[lane + 32 * i] = v[i];
+  }
+}
+
 // Three-way class of the same tile: skipped / partial (needs an element mask) / unmasked.
 __device__ __forceinline__ int classify_tile(const MaskDesc& md, int bh_mask, int n, int ms, int me,
                                              int tile_n) {

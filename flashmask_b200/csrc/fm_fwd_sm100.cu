@@ -369,8 +369,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (!ok) break;
           int* dst = reinterpret_cast<int*>(smem + Cfg::OFF_BND + bslot * Cfg::BND_BYTES);
           const int32_t* src = md.mask + ((size_t)bh_mask * p.Sk + j0) * md.ncols;
-          const int valid = min(128, p.Sk - j0) * md.ncols;
-          for (int x = lane; x < 128 * md.ncols; x += 32) dst[x] = x < valid ? __ldg(src + x) : 0;
+          stage_bounds(dst, src, 128, min(128, p.Sk - j0), md.ncols, lane);
           mbar_arrive(bar(Cfg::B_BNDFULL + bslot));
           ++nbnd;
         }

@@ -2,6 +2,8 @@
 // then (Q tile, K tile) classification + surviving-tile counts, and the exact
 // unmasked-pair count used as the work measure.  Integer, HBM-bound work:
 // coalesced vector loads, one warp per K tile / per Q tile.
+#include <cstdlib>
+
 #include "fm_attn_params.cuh"
 
 namespace fm {
@@ -106,10 +108,11 @@ __global__ void __launch_bounds__(256) count_visible_kernel(MaskDesc md, int64_t
 //      index order, so operands shared between neighbouring tiles still meet in L2.
 // smem: work[E], order[E], hist/start[FM_ORDER_BUCKETS + 1], red[32], class[E] bytes.
 constexpr int FM_ORDER_BUCKETS = 8;
+constexpr int FM_PERSIST_MAX_ITEMS = 96;
 
 __global__ void __launch_bounds__(1024) launch_order_kernel(MaskDesc md, int axis, int block_rows, int tile_n,
                                                             int n_units, int n_other, int rep_h, int rep_b,
-                                                            int heads, int32_t* __restrict__ out) {
+                                                            int heads, int item_mult, int32_t* __restrict__ out) {
   extern __shared__ int32_t sm[];
   const int E = md.BHm * n_units;
   int32_t* swork = sm;
@@ -122,6 +125,7 @@ __global__ void __launch_bounds__(1024) launch_order_kernel(MaskDesc md, int axi
   int2* table = reinterpret_cast<int2*>(out);
   int32_t* gwork = out + 2 * (size_t)n_cta;
   int32_t* gorder = gwork + E;
+  if (tid < 4) gorder[E + tid] = 0;   // counters of the persistent kernels that walk this table
 
   for (int e = warp; e < E; e += 32) {
     const int bh = e / n_units, u = e % n_units;
@@ -143,13 +147,23 @@ __global__ void __launch_bounds__(1024) launch_order_kernel(MaskDesc md, int axi
   __syncthreads();
 
   int mx = 0;
-  for (int e = tid; e < E; e += 1024) mx = max(mx, swork[e]);
+  long long total = 0;
+  for (int e = tid; e < E; e += 1024) { mx = max(mx, swork[e]); total += swork[e]; }
 #pragma unroll
-  for (int o = 16; o; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  if (lane == 0) sred[warp] = mx;
+  for (int o = 16; o; o >>= 1) {
+    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    total += __shfl_xor_sync(0xffffffffu, total, o);
+  }
+  __shared__ long long stot[32];
+  if (lane == 0) { sred[warp] = mx; stot[warp] = total; }
   __syncthreads();
   mx = 0;
-  for (int w = 0; w < 32; ++w) mx = max(mx, sred[w]);
+  total = 0;
+  for (int w = 0; w < 32; ++w) { mx = max(mx, sred[w]); total += stot[w]; }
+  // [E+2]: 1 while a unit averages at most FM_PERSIST_MAX_ITEMS work items, the range in which the
+  // persistent backward variant (which hides the per-unit prologue and epilogue at a slightly slower
+  // main loop) was measured faster; information for the host, the kernels do not read it
+  if (tid == 0) gorder[E + 2] = total * item_mult <= (long long)FM_PERSIST_MAX_ITEMS * E ? 1 : 0;
   for (int e = tid; e < E; e += 1024) {
     const int k = (int)(((long long)(mx - swork[e]) * FM_ORDER_BUCKETS) / (mx + 1));  // 0 = heaviest class
     sclass[e] = (uint8_t)k;
@@ -189,10 +203,11 @@ __global__ void __launch_bounds__(1024) launch_order_kernel(MaskDesc md, int axi
 using namespace fm;
 
 int fm::launch_order_build(const MaskDesc& md, int axis, int block_rows, int tile_n, int n_units, int n_other,
-                           int rep_h, int rep_b, int heads, int32_t* out, cudaStream_t s) {
+                           int rep_h, int rep_b, int heads, int item_mult, int32_t* out, cudaStream_t s) {
   const int E = md.BHm * n_units;
   const size_t smem = sizeof(int32_t) * (2 * (size_t)E + FM_ORDER_BUCKETS + 1 + 32) + (size_t)E;
-  launch_order_kernel<<<1, 1024, smem, s>>>(md, axis, block_rows, tile_n, n_units, n_other, rep_h, rep_b, heads, out);
+  launch_order_kernel<<<1, 1024, smem, s>>>(md, axis, block_rows, tile_n, n_units, n_other, rep_h, rep_b, heads,
+                                            item_mult, out);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }

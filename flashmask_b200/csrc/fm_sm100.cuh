@@ -65,6 +65,31 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   }
 }
 
+// The same for waits that last a whole work unit (scheduler and epilogue warps): the wait is
+// handed to the barrier hardware with a suspend-time hint, so the waiting warp issues next to
+// nothing and takes no issue slots from the warps of its scheduler.
+__device__ __forceinline__ bool mbar_try_wait_suspended(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_idle(uint32_t bar, uint32_t parity, const WaitCtx& w) {
+  for (;;) {
+    if (mbar_try_wait_suspended(bar, parity, 20000u)) return true;
+    if (*w.abort_flag) return false;
+    if (global_timer_ns() > w.deadline_ns) {
+      *w.abort_flag = 1;
+      return false;
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // TMA: 4-D tiled load global -> shared, completion on an mbarrier (no multicast)
 // ---------------------------------------------------------------------------

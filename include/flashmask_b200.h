@@ -168,18 +168,17 @@ FM_API int fm_fwd(const fm_attn_args* args, void* stream);
  * Only the problem geometry of `args` is read (B, Hq, Hkv, mask_B, Hm, Sq, Sk,
  * ncols, causal, d, dv, minmax, tile_n).  With E = mask_B*Hm*units and
  * N = E * (heads/Hm) * (B/mask_B) = the number of CTAs of the kernel:
- *   fm_launch_order_ints  number of int32 `out` must hold, 2*N + 2*E, or 0
+ *   fm_launch_order_ints  number of int32 `out` must hold, 2*N + 2*E + 4, or 0
  *                         when the kernel variant for (d, dv) takes no order,
- *                         there is no mask tensor, E > 4096, or an order is not
- *                         expected to pay: every CTA reads its table entry before
- *                         it can start, so the forward is always ordered, the
- *                         dK/dV kernel while N <= 8 waves of the 148 SMs, the dQ
- *                         kernel never (FLASHMASK_B200_ORDER_FORCE=1 in the
- *                         environment builds all three).
+ *                         there is no mask tensor, or E > 4096.
  *   fm_launch_order       out[2L], out[2L+1] = (unit, b*heads + head) of the
  *                         L-th CTA in dispatch order; then E ints of work per
  *                         unit (mask_b, mask_h, unit flattened) and E ints of
- *                         the units by (class, index).  `out` is 8-byte
+ *                         the units by (class, index), then 4 ints of counters
+ *                         that the backward kernels, which walk their table
+ *                         persistently (one CTA per SM fetching entries through
+ *                         a counter), advance and rewind on every launch: one
+ *                         table serves one stream at a time.  `out` is 8-byte
  *                         aligned.  Pass it as the matching *_order field of
  *                         later fm_fwd / fm_bwd calls with the same mask and
  *                         the same B, Hq, Hkv.

@@ -190,11 +190,14 @@ def test_deterministic_bitwise(fwd_variant):
             assert torch.equal(a[n], b[n]), n
 
 
+@pytest.mark.parametrize("persist", ["0", "1"])
 @pytest.mark.parametrize("kind,mask_b,hm", [("causal_doc", 2, 1), ("four_column", 1, 2), ("share_question", 2, 2),
                                             ("bidir_doc", 1, 1)])
-def test_launch_order_changes_no_bit(kind, mask_b, hm, monkeypatch):
-    """The longest-work-first launch order only permutes which CTA runs which tile:
-    results are bitwise those of the index order, for every mask batch / head broadcast."""
+def test_launch_order_changes_no_bit(kind, mask_b, hm, persist, monkeypatch):
+    """The longest-work-first launch order only permutes which CTA runs which tile, and the
+    persistent backward variant only changes which CTA runs which unit: results are bitwise
+    those of the index order, for every mask batch / head broadcast and both backward variants."""
+    monkeypatch.setenv("FLASHMASK_B200_PERSIST", persist)
     B, S, Hq, Hkv = 2, 1024, 8, 2
     idx_np, causal = _mask(kind, B, S, S, 33)
     idx_np = np.ascontiguousarray(idx_np[:mask_b]).copy()

@@ -128,20 +128,22 @@ def test_launch_order_bit_exact(Sq, Sk, mask_b, hm, monkeypatch):
             rep_h, rep_b = heads // hm, B // mask_b
             n_cta = work.size * rep_h * rep_b
             n = lib.fm_launch_order_ints(C.byref(a), which)
-            assert n == 2 * n_cta + 2 * work.size, (name, which)
+            assert n == 2 * n_cta + 2 * work.size + 4, (name, which)
             out = torch.full((n,), -1, dtype=torch.int32, device="cuda")
             _lib.check(lib.fm_launch_order(C.byref(a), which, out.data_ptr(), None), "fm_launch_order")
             out = out.cpu().numpy()
             order, table = _expected_launch_table(work, n_units, hm, mask_b, rep_h, rep_b, heads)
             assert np.array_equal(out[2 * n_cta:2 * n_cta + work.size], work), (name, which)
-            assert np.array_equal(out[2 * n_cta + work.size:], order), (name, which)
+            assert np.array_equal(out[2 * n_cta + work.size:2 * n_cta + 2 * work.size], order), (name, which)
+            # behind the table: two counters at zero, the variant flag (persistent iff units are short), a pad
+            assert out[-4] == 0 and out[-3] == 0 and out[-1] == 0 and out[-2] in (0, 1)
+            if which != _lib.FM_ORDER_FWD:
+                mult = 2 if which == _lib.FM_ORDER_BWD_DQ else Hq // Hkv
+                assert out[-2] == int(int(work.sum()) * mult <= 96 * work.size), (name, which)
             got = out[:2 * n_cta].reshape(-1, 2)
             assert np.array_equal(got, table), (name, which)
             assert len({(int(u), int(h)) for u, h in got}) == n_cta == n_units * heads * B
-    # no order where it does not pay, where the kernel variant takes none, or without a mask tensor
-    monkeypatch.delenv("FLASHMASK_B200_ORDER_FORCE")
-    assert lib.fm_launch_order_ints(C.byref(a), _lib.FM_ORDER_BWD_DQ) == 0
-    assert lib.fm_launch_order_ints(C.byref(a), _lib.FM_ORDER_FWD) > 0
+    # no order where the kernel variant takes none, or without a mask tensor
     a.d = a.dv = 64
     assert lib.fm_launch_order_ints(C.byref(a), _lib.FM_ORDER_FWD) == 0
     a.d = a.dv = 128
