@@ -59,20 +59,31 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.samples.append(line.strip())
+            self.samples.append((time.perf_counter(), line.strip()))
+
+    def mark(self):
+        """Start of the timed region (the sampler itself is started before the warm-up: nvidia-smi
+        takes a few hundred ms to deliver its first sample)."""
+        self.t_mark = time.perf_counter()
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        t_end = time.perf_counter()
         time.sleep(0.15)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=2)
         except Exception:
             pass
+        t_mark = getattr(self, "t_mark", 0.0)
+        inside = [l for t, l in self.samples if t_mark <= t <= t_end + 0.1]
+        window = "timed region"
+        if not inside:      # a timed region shorter than the sampling period: the warm-up ran the same load
+            inside, window = [l for _, l in self.samples], "warm-up + timed region"
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
+        for s in inside:
             f = [x.strip() for x in s.split(",")]
             if len(f) < 6:
                 continue
@@ -84,7 +95,8 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm),
+                "window": window}
 
 
 # ---------------------------------------------------------------------------
@@ -164,14 +176,15 @@ def run_cp(args, rank, local_rank, world):
     def fresh():
         return q.detach().clone(), k.detach().clone(), v.detach().clone(), do
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(max(3, args.warmup)):
         step(*fresh())
     barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ins = [fresh() for _ in range(args.steps)]
     barrier()
+    sampler.mark()
     e0.record()
     for i in range(args.steps):
         step(*ins[i])
@@ -319,12 +332,13 @@ def main():
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(max(3, args.warmup)):
         step_device()
     barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.mark()
     e0.record()
     for _ in range(args.steps):
         step_device()
