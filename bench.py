@@ -318,9 +318,9 @@ def main():
         info_b = info_f if (info_f is None or btn == ftn) else fm.prepare_mask(idx, w.Sq, w.causal, btm, btn)
         out, lse = fm._flash_attn_fwd(q, k, v, idx, causal=w.causal, mask_info=info_f)
         res = fm._flash_attn_bwd(q, k, v, out, do, lse, idx, causal=w.causal, mask_info=info_b)
-        # launch-order tables are built once per mask info, i.e. once per step here (1 kernel each)
-        n_launch["order"] = sum(t is not None for i in {id(info_f): info_f, id(info_b): info_b}.values()
-                                if i is not None for t in i.orders.values())
+        # launch tables are built once per mask info, i.e. once per step here (one launch for all three)
+        n_launch["order"] = sum(1 for i in {id(info_f): info_f, id(info_b): info_b}.values()
+                                if i is not None and any(t is not None for t in i.orders.values()))
         return res
 
     # mask scan (+1 if fwd and bwd tile widths differ) + launch-order tables + forward + (preprocess, dK/dV, dQ)

@@ -56,6 +56,7 @@ SIGNATURES = {
     "fm_fwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "fm_launch_order_ints": (C.c_int64, [C.POINTER(AttnArgs), C.c_int]),
     "fm_launch_order": (C.c_int, [C.POINTER(AttnArgs), C.c_int, C.c_void_p, C.c_void_p]),
+    "fm_launch_orders": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "fm_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(AttnArgs)]),
     "fm_bwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "fm_kernel_status": (C.c_int, [C.POINTER(C.c_int), C.c_int]),

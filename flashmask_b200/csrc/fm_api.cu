@@ -242,20 +242,40 @@ static void attach_bwd_tables(const fm_attn_args* a, AttnKParams* p) {
   }
 }
 
-extern "C" int fm_launch_order(const fm_attn_args* a, int which, int32_t* out, void* stream) {
-  OrderGeom g;
-  FM_REQUIRE(a && out, FM_ERR_INVALID_ARGUMENT, "fm_launch_order: NULL argument");
-  FM_REQUIRE(order_geometry(a, which, &g), FM_ERR_UNSUPPORTED,
-             "fm_launch_order: no order for this kernel variant / mask (fm_launch_order_ints returned 0)");
-  FM_REQUIRE(a->minmax && a->tile_n == 128, FM_ERR_INVALID_ARGUMENT,
-             "fm_launch_order: minmax must be prepared with tile_n = 128");
-  FM_REQUIRE(((uintptr_t)out & 7) == 0, FM_ERR_INVALID_ARGUMENT, "fm_launch_order: out must be 8-byte aligned");
-  MaskDesc md{a->mask, a->minmax, a->ncols, a->causal, a->Hm, a->mask_B, fm_mask_nblk_pad(a->Sk, 128),
-              a->mask_B * a->Hm, a->Sq, a->Sk};
+static OrderJob order_job(const fm_attn_args* a, int which, const OrderGeom& g, int32_t* out) {
   // work items per unit of work: two 64-key halves per K tile (dQ), one per q head of the group (dK/dV)
   const int item_mult = which == FM_ORDER_BWD_DQ ? 2 : (which == FM_ORDER_BWD_DKDV ? a->Hq / a->Hkv : 1);
-  return launch_order_build(md, g.axis, g.block_rows, 128, g.n_units, g.n_other, g.rep_h, g.rep_b, g.heads, item_mult,
-                            out, (cudaStream_t)stream);
+  return OrderJob{g.axis, g.block_rows, g.n_units, g.n_other, g.rep_h, g.rep_b, g.heads, item_mult, out};
+}
+
+extern "C" int fm_launch_order(const fm_attn_args* a, int which, int32_t* out, void* stream) {
+  int32_t* outs[3] = {nullptr, nullptr, nullptr};
+  FM_REQUIRE(which >= 0 && which < 3, FM_ERR_INVALID_ARGUMENT, "fm_launch_order: unknown kernel %d", which);
+  FM_REQUIRE(out != nullptr, FM_ERR_INVALID_ARGUMENT, "fm_launch_order: NULL argument");
+  outs[which] = out;
+  return fm_launch_orders(a, outs[0], outs[1], outs[2], stream);
+}
+
+extern "C" int fm_launch_orders(const fm_attn_args* a, int32_t* out_fwd, int32_t* out_dq, int32_t* out_dkdv,
+                                void* stream) {
+  FM_REQUIRE(a && (out_fwd || out_dq || out_dkdv), FM_ERR_INVALID_ARGUMENT, "fm_launch_orders: NULL argument");
+  FM_REQUIRE(a->minmax && a->tile_n == 128, FM_ERR_INVALID_ARGUMENT,
+             "fm_launch_orders: minmax must be prepared with tile_n = 128");
+  int32_t* outs[3] = {out_fwd, out_dq, out_dkdv};
+  OrderJobs jobs;
+  int n = 0;
+  for (int which = 0; which < 3; ++which) {
+    if (!outs[which]) continue;
+    OrderGeom g;
+    FM_REQUIRE(order_geometry(a, which, &g), FM_ERR_UNSUPPORTED,
+               "fm_launch_orders: no order for kernel %d with this variant / mask (fm_launch_order_ints returned 0)",
+               which);
+    FM_REQUIRE(((uintptr_t)outs[which] & 7) == 0, FM_ERR_INVALID_ARGUMENT, "fm_launch_orders: out must be 8-byte aligned");
+    jobs.job[n++] = order_job(a, which, g, outs[which]);
+  }
+  MaskDesc md{a->mask, a->minmax, a->ncols, a->causal, a->Hm, a->mask_B, fm_mask_nblk_pad(a->Sk, 128),
+              a->mask_B * a->Hm, a->Sq, a->Sk};
+  return launch_order_build(md, 128, jobs, n, (cudaStream_t)stream);
 }
 
 extern "C" size_t fm_bwd_workspace_bytes(const fm_attn_args* a) {

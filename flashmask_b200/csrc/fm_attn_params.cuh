@@ -38,7 +38,11 @@ __device__ __forceinline__ OrderedCta ordered_cta(const int32_t* table, int head
 
 // Units a launch table may cover (one CTA builds it, the unit work staged in shared memory).
 constexpr int FM_ORDER_MAX_UNITS = 4096;
-int launch_order_build(const MaskDesc& md, int axis, int block_rows, int tile_n, int n_units, int n_other,
-                       int rep_h, int rep_b, int heads, int item_mult, int32_t* out, cudaStream_t s);
+// One table to build: the ordered axis (0 rows / 1 key tiles), rows per unit, units, extent of the
+// other axis, repeats, heads of the kernel, work items per unit of work, destination.
+struct OrderJob { int axis, block_rows, n_units, n_other, rep_h, rep_b, heads, item_mult; int32_t* out; };
+struct OrderJobs { OrderJob job[3]; };
+// Builds up to three tables in one launch (one CTA each).
+int launch_order_build(const MaskDesc& md, int tile_n, const OrderJobs& jobs, int n_jobs, cudaStream_t s);
 
 }  // namespace fm

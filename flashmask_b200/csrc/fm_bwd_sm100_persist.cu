@@ -297,16 +297,9 @@ bwd_sm100_persist_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __g
       const int s = j & 1;
       ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_INFOREADY + s), (uint32_t)(j >> 1) & 1u, wc));
       if (!ok) break;
-#ifdef FM_VAR_A
-      const int cnt = __shfl_sync(0xffffffffu, infos[s * 8 + 3], 0);
-      if (cnt < 0) break;
-      const int b = __shfl_sync(0xffffffffu, infos[s * 8 + 0], 0), head = __shfl_sync(0xffffffffu, infos[s * 8 + 1], 0);
-      const int row0 = __shfl_sync(0xffffffffu, infos[s * 8 + 2], 0), bh_mask = __shfl_sync(0xffffffffu, infos[s * 8 + 4], 0);
-#else
       const int cnt = infos[s * 8 + 3];
       if (cnt < 0) break;
       const int b = infos[s * 8 + 0], head = infos[s * 8 + 1], row0 = infos[s * 8 + 2], bh_mask = infos[s * 8 + 4];
-#endif
       const int hk = (MODE == MODE_DKDV) ? head : head / G;
       const int hq0 = (MODE == MODE_DKDV) ? head * G : head;
       const uint16_t* list = lists + s * Cfg::LIST_MAX;

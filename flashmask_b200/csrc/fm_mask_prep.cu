@@ -2,6 +2,7 @@
 // then (Q tile, K tile) classification + surviving-tile counts, and the exact
 // unmasked-pair count used as the work measure.  Integer, HBM-bound work:
 // coalesced vector loads, one warp per K tile / per Q tile.
+#include <algorithm>
 #include <cstdlib>
 
 #include "fm_attn_params.cuh"
@@ -110,9 +111,11 @@ __global__ void __launch_bounds__(256) count_visible_kernel(MaskDesc md, int64_t
 constexpr int FM_ORDER_BUCKETS = 8;
 constexpr int FM_PERSIST_MAX_ITEMS = 96;
 
-__global__ void __launch_bounds__(1024) launch_order_kernel(MaskDesc md, int axis, int block_rows, int tile_n,
-                                                            int n_units, int n_other, int rep_h, int rep_b,
-                                                            int heads, int item_mult, int32_t* __restrict__ out) {
+__global__ void __launch_bounds__(1024) launch_order_kernel(MaskDesc md, int tile_n, OrderJobs jobs) {
+  const OrderJob& jb = jobs.job[blockIdx.x];   // one CTA per table
+  const int axis = jb.axis, block_rows = jb.block_rows, n_units = jb.n_units, n_other = jb.n_other;
+  const int rep_h = jb.rep_h, rep_b = jb.rep_b, heads = jb.heads, item_mult = jb.item_mult;
+  int32_t* __restrict__ out = jb.out;
   extern __shared__ int32_t sm[];
   const int E = md.BHm * n_units;
   int32_t* swork = sm;
@@ -202,12 +205,13 @@ __global__ void __launch_bounds__(1024) launch_order_kernel(MaskDesc md, int axi
 
 using namespace fm;
 
-int fm::launch_order_build(const MaskDesc& md, int axis, int block_rows, int tile_n, int n_units, int n_other,
-                           int rep_h, int rep_b, int heads, int item_mult, int32_t* out, cudaStream_t s) {
-  const int E = md.BHm * n_units;
-  const size_t smem = sizeof(int32_t) * (2 * (size_t)E + FM_ORDER_BUCKETS + 1 + 32) + (size_t)E;
-  launch_order_kernel<<<1, 1024, smem, s>>>(md, axis, block_rows, tile_n, n_units, n_other, rep_h, rep_b, heads,
-                                            item_mult, out);
+int fm::launch_order_build(const MaskDesc& md, int tile_n, const OrderJobs& jobs, int n_jobs, cudaStream_t s) {
+  size_t smem = 0;
+  for (int i = 0; i < n_jobs; ++i) {
+    const size_t E = (size_t)md.BHm * jobs.job[i].n_units;
+    smem = std::max(smem, sizeof(int32_t) * (2 * E + FM_ORDER_BUCKETS + 1 + 32) + E);
+  }
+  launch_order_kernel<<<n_jobs, 1024, smem, s>>>(md, tile_n, jobs);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }

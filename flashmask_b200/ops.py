@@ -82,23 +82,30 @@ def prepare_mask(idx: torch.Tensor, Sq: int, causal: bool, tile_m: int, tile_n: 
 
 
 def _launch_order(a: "_lib.AttnArgs", info: FlashMaskInfo, which: int, ref: torch.Tensor) -> Optional[int]:
-    """Device pointer of the launch order ``which`` (FM_ORDER_*) for this mask and kernel
-    variant, or None when the variant takes none.  Built once per FlashMaskInfo
-    (one small kernel on the current stream).  FLASHMASK_B200_ORDER=0 turns all orders off,
-    a comma list out of fwd,dq,dkdv keeps only those (A/B runs)."""
+    """Device pointer of the launch table ``which`` (FM_ORDER_*) for this mask and kernel
+    variant, or None when the variant takes none.  The tables of all three kernels are built
+    together on first use, once per FlashMaskInfo (ONE small launch on the current stream).
+    FLASHMASK_B200_ORDER=0 turns all tables off, a comma list out of fwd,dq,dkdv keeps only
+    those (A/B runs)."""
     sel = os.environ.get("FLASHMASK_B200_ORDER", "1")
-    if sel != "1" and ("fwd", "dq", "dkdv")[which] not in sel.split(","):
+    names = ("fwd", "dq", "dkdv")
+    wanted = [w for w in range(3) if sel == "1" or names[w] in sel.split(",")]
+    if which not in wanted:
         return None
-    key = (which, a.d, a.dv, a.Sq, a.B, a.Hq, a.Hkv)
-    if key not in info.orders:
+    geom = (a.d, a.dv, a.Sq, a.B, a.Hq, a.Hkv)
+    if (which,) + geom not in info.orders:
         lib = _lib.load()
-        n = lib.fm_launch_order_ints(C.byref(a), which)
-        buf = None
-        if n:
-            buf = torch.empty(n, dtype=torch.int32, device=ref.device)
-            _lib.check(lib.fm_launch_order(C.byref(a), which, buf.data_ptr(), _stream(ref)), "fm_launch_order")
-        info.orders[key] = buf
-    buf = info.orders[key]
+        bufs = [None, None, None]
+        for w in wanted:
+            if (w,) + geom in info.orders:
+                continue
+            n = lib.fm_launch_order_ints(C.byref(a), w)
+            bufs[w] = torch.empty(n, dtype=torch.int32, device=ref.device) if n else None
+            info.orders[(w,) + geom] = bufs[w]
+        if any(t is not None for t in bufs):
+            _lib.check(lib.fm_launch_orders(C.byref(a), *[None if t is None else t.data_ptr() for t in bufs],
+                                            _stream(ref)), "fm_launch_orders")
+    buf = info.orders[(which,) + geom]
     return None if buf is None else buf.data_ptr()
 
 

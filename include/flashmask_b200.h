@@ -191,6 +191,9 @@ FM_API int fm_fwd(const fm_attn_args* args, void* stream);
 #define FM_ORDER_BWD_DKDV 2
 FM_API int64_t fm_launch_order_ints(const fm_attn_args* args, int which);
 FM_API int fm_launch_order(const fm_attn_args* args, int which, int32_t* out, void* stream);
+/* The same for up to three kernels in ONE launch (a NULL pointer skips that kernel's table). */
+FM_API int fm_launch_orders(const fm_attn_args* args, int32_t* out_fwd, int32_t* out_dq, int32_t* out_dkdv,
+                            void* stream);
 
 /* Device-side status of the kernels that wait on barriers (the tcgen05
  * variants): every wait is bounded, and a wait that ran out makes its CTA

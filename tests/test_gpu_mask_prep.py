@@ -143,6 +143,15 @@ def test_launch_order_bit_exact(Sq, Sk, mask_b, hm, monkeypatch):
             got = out[:2 * n_cta].reshape(-1, 2)
             assert np.array_equal(got, table), (name, which)
             assert len({(int(u), int(h)) for u, h in got}) == n_cta == n_units * heads * B
+    # all three tables in one launch are those of three single launches
+    sizes = [lib.fm_launch_order_ints(C.byref(a), w) for w in range(3)]
+    single = [torch.empty(n, dtype=torch.int32, device="cuda") for n in sizes]
+    for w in range(3):
+        _lib.check(lib.fm_launch_order(C.byref(a), w, single[w].data_ptr(), None), "fm_launch_order")
+    fused = [torch.full((n,), -1, dtype=torch.int32, device="cuda") for n in sizes]
+    _lib.check(lib.fm_launch_orders(C.byref(a), *[t.data_ptr() for t in fused], None), "fm_launch_orders")
+    for w in range(3):
+        assert torch.equal(single[w], fused[w]), w
     # no order where the kernel variant takes none, or without a mask tensor
     a.d = a.dv = 64
     assert lib.fm_launch_order_ints(C.byref(a), _lib.FM_ORDER_FWD) == 0
