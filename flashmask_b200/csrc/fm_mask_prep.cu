@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(256) count_visible_kernel(MaskDesc md, int64_t
 constexpr int FM_ORDER_BUCKETS = 8;
 constexpr int FM_PERSIST_MAX_ITEMS = 96;
 
-__global__ void __launch_bounds__(1024) launch_order_kernel(MaskDesc md, int tile_n, OrderJobs jobs) {
+__global__ void __launch_bounds__(1024) launch_order_kernel(MaskDesc md, int tile_n, OrderJobs jobs, int n_classes) {
   const OrderJob& jb = jobs.job[blockIdx.x];   // one CTA per table
   const int axis = jb.axis, block_rows = jb.block_rows, n_units = jb.n_units, n_other = jb.n_other;
   const int rep_h = jb.rep_h, rep_b = jb.rep_b, heads = jb.heads, item_mult = jb.item_mult;
@@ -168,7 +168,7 @@ __global__ void __launch_bounds__(1024) launch_order_kernel(MaskDesc md, int til
   // main loop) was measured faster; information for the host, the kernels do not read it
   if (tid == 0) gorder[E + 2] = total * item_mult <= (long long)FM_PERSIST_MAX_ITEMS * E ? 1 : 0;
   for (int e = tid; e < E; e += 1024) {
-    const int k = (int)(((long long)(mx - swork[e]) * FM_ORDER_BUCKETS) / (mx + 1));  // 0 = heaviest class
+    const int k = (int)(((long long)(mx - swork[e]) * n_classes) / (mx + 1));  // 0 = heaviest class
     sclass[e] = (uint8_t)k;
     atomicAdd(&sstart[k + 1], 1);
   }
@@ -211,7 +211,9 @@ int fm::launch_order_build(const MaskDesc& md, int tile_n, const OrderJobs& jobs
     const size_t E = (size_t)md.BHm * jobs.job[i].n_units;
     smem = std::max(smem, sizeof(int32_t) * (2 * E + FM_ORDER_BUCKETS + 1 + 32) + E);
   }
-  launch_order_kernel<<<n_jobs, 1024, smem, s>>>(md, tile_n, jobs);
+  int n_classes = FM_ORDER_BUCKETS;
+  if (const char* e = getenv("FLASHMASK_B200_CLASSES")) n_classes = std::min(FM_ORDER_BUCKETS, std::max(1, atoi(e)));
+  launch_order_kernel<<<n_jobs, 1024, smem, s>>>(md, tile_n, jobs, n_classes);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }
