@@ -111,12 +111,29 @@ __global__ void __launch_bounds__(256) count_visible_kernel(MaskDesc md, int64_t
 constexpr int FM_ORDER_BUCKETS = 8;
 constexpr int FM_PERSIST_MAX_ITEMS = 96;
 
-__global__ void __launch_bounds__(1024) launch_order_kernel(MaskDesc md, int tile_n, OrderJobs jobs, int n_classes) {
+__global__ void __launch_bounds__(1024) launch_order_kernel(MaskDesc md_in, int tile_n, OrderJobs jobs, int n_classes,
+                                                            int stage_ints, int work_off) {
   const OrderJob& jb = jobs.job[blockIdx.x];   // one CTA per table
   const int axis = jb.axis, block_rows = jb.block_rows, n_units = jb.n_units, n_other = jb.n_other;
   const int rep_h = jb.rep_h, rep_b = jb.rep_b, heads = jb.heads, item_mult = jb.item_mult;
   int32_t* __restrict__ out = jb.out;
-  extern __shared__ int32_t sm[];
+  extern __shared__ int32_t sm_all[];
+  // the per-tile reductions of the whole mask are staged in shared memory first (when they fit):
+  // classifying a unit then costs no global round trip
+  MaskDesc md = md_in;
+  if (stage_ints) {
+    const int row4 = (md.BHm * md.nblk_pad) >> 2;                      // int4 per reduction
+    const uint32_t which = md.ncols == 1 ? 0x03u : (md.ncols == 4 ? 0xFFu : (md.causal ? 0x0Fu : 0xC3u));
+    for (int w = 0; w < 8; ++w) {
+      if (!(which >> w & 1u)) continue;
+      const int4* src = reinterpret_cast<const int4*>(md_in.minmax) + (size_t)w * row4;
+      int4* dst = reinterpret_cast<int4*>(sm_all) + (size_t)w * row4;
+      for (int i = threadIdx.x; i < row4; i += 1024) dst[i] = __ldg(src + i);
+    }
+    md.minmax = sm_all;
+    __syncthreads();
+  }
+  int32_t* sm = sm_all + work_off;
   const int E = md.BHm * n_units;
   int32_t* swork = sm;
   int32_t* sorder = sm + E;
@@ -213,7 +230,14 @@ int fm::launch_order_build(const MaskDesc& md, int tile_n, const OrderJobs& jobs
   }
   int n_classes = FM_ORDER_BUCKETS;
   if (const char* e = getenv("FLASHMASK_B200_CLASSES")) n_classes = std::min(FM_ORDER_BUCKETS, std::max(1, atoi(e)));
-  launch_order_kernel<<<n_jobs, 1024, smem, s>>>(md, tile_n, jobs, n_classes);
+  // staging area for the reductions: 8 x BHm x nblk_pad ints, only when that stays small
+  const size_t stage_ints = 8 * (size_t)md.BHm * md.nblk_pad;
+  const int staged = (stage_ints * 4 + smem <= 96 * 1024 && (reinterpret_cast<uintptr_t>(md.minmax) & 15) == 0)
+                         ? (int)stage_ints : 0;
+  smem += (size_t)staged * 4;
+  if (smem > 48 * 1024)
+    FM_CUDA_TRY(cudaFuncSetAttribute(launch_order_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+  launch_order_kernel<<<n_jobs, 1024, smem, s>>>(md, tile_n, jobs, n_classes, staged, staged);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }
