@@ -215,6 +215,31 @@ def test_launch_order_changes_no_bit(kind, mask_b, hm, persist, monkeypatch):
         assert torch.equal(a[n], b[n]), n
 
 
+def test_launch_tables_are_reusable():
+    """One FlashMaskInfo (one set of launch tables, whose unit counters the persistent backward
+    advances and rewinds) serves many launches: every repeat gives the first result."""
+    B, S, Hq, Hkv = 1, 2048, 4, 2
+    idx_np, causal = _mask("causal_doc", B, S, S, 9)
+    q, k, v, do, _ = make_inputs(B, S, S, Hq, Hkv, 128, 128, 9)
+    q, k, v, do = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    idx = torch.from_numpy(np.ascontiguousarray(idx_np).copy()).cuda()
+    info = fm.prepare_mask(idx, S, causal, 128, 128)
+    out, lse = fm._flash_attn_fwd(q, k, v, idx, causal=causal, mask_info=info)
+    first = fm._flash_attn_bwd(q, k, v, out, do, lse, idx, causal=causal, mask_info=info)
+    assert any(t is not None for t in info.orders.values())
+    for _ in range(4):
+        out2, lse2 = fm._flash_attn_fwd(q, k, v, idx, causal=causal, mask_info=info)
+        again = fm._flash_attn_bwd(q, k, v, out, do, lse, idx, causal=causal, mask_info=info)
+        assert torch.equal(out, out2) and torch.equal(lse, lse2)
+        for a, b in zip(first[:3], again[:3]):
+            assert torch.equal(a, b)
+    # the counters behind the backward tables are back at zero
+    torch.cuda.synchronize()
+    for key, t in info.orders.items():
+        if t is not None and key[0] != 0:
+            assert t[-4:-2].tolist() == [0, 0], key
+
+
 def test_layout_invariance(fwd_variant):
     """Contiguous vs permuted storage of q/k/v give bitwise equal results
     (reference: tests/torch/test_flashmask.py:354-396)."""
