@@ -34,6 +34,9 @@ int fwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s
 bool bwd_sm100_supported(const fm_attn_args* a);
 int bwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s);
 int bwd_sm100_persist_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s);
+bool fwd_sm100_persist_supported(const fm_attn_args* a);
+int fwd_sm100_persist_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s);
+int fwd_sm100_persist_status(int* out, bool reset);
 int bwd_sm100_persist_status(int* out, bool reset);
 size_t bwd_sm100_workspace_bytes(const fm_attn_args* a);
 
@@ -148,6 +151,8 @@ static int run_bwd_kernels(const fm_attn_args* a, const AttnKParams& p, cudaStre
   return rc;
 }
 
+static bool attach_fwd_table(const fm_attn_args* a, AttnKParams* p);
+
 extern "C" int fm_fwd_tile_shape(int d, int dv, int* tile_m, int* tile_n) {
   FM_REQUIRE(tile_m && tile_n, FM_ERR_INVALID_ARGUMENT, "fm_fwd_tile_shape: NULL output");
   if (fwd_uses_sm100(d, dv)) { *tile_m = 128; *tile_n = 128; return FM_OK; }
@@ -175,7 +180,15 @@ extern "C" int fm_fwd(const fm_attn_args* a, void* stream) {
   AttnKParams p;
   fill_kparams(a, &p, false);
   p.md.nblk_pad = fm_mask_nblk_pad(a->Sk, tn);
-  if (fwd_uses_sm100(a->d, a->dv) && fwd_sm100_supported(a)) return fwd_sm100_launch(p, a, (cudaStream_t)stream);
+  if (fwd_uses_sm100(a->d, a->dv) && fwd_sm100_supported(a)) {
+    // with a launch table (a mask tensor) the persistent variant can walk it (FLASHMASK_B200_FWD_PERSIST=1);
+    // the one-unit-per-CTA kernel reads its table entry at CTA start
+    const char* pe = getenv("FLASHMASK_B200_FWD_PERSIST");
+    if (p.fwd_order && pe && pe[0] == '1' && pe[1] == 0 && fwd_sm100_persist_supported(a) &&
+        attach_fwd_table(a, &p))
+      return fwd_sm100_persist_launch(p, a, (cudaStream_t)stream);
+    return fwd_sm100_launch(p, a, (cudaStream_t)stream);
+  }
   FM_REQUIRE(!fwd_uses_sm100(a->d, a->dv), FM_ERR_INVALID_ARGUMENT,
              "fm_fwd: q/k/v must be 16-byte aligned");
   return fwd_mma_launch(p, a->dtype, (cudaStream_t)stream);
@@ -223,7 +236,17 @@ extern "C" int64_t fm_launch_order_ints(const fm_attn_args* a, int which) {
   return 2 * g.n_cta + 2 * g.E + 4;
 }
 
-// The counters of the persistent backward kernels live behind the table and the two unit arrays.
+// The counters of the persistent kernels live behind the table and the two unit arrays.
+static bool attach_fwd_table(const fm_attn_args* a, AttnKParams* p) {
+  OrderGeom g;
+  p->fwd_sched = nullptr;
+  p->fwd_ncta = 0;
+  if (!p->fwd_order || !order_geometry_any(a, FM_ORDER_FWD, &g)) return false;
+  p->fwd_ncta = (int)g.n_cta;
+  p->fwd_sched = const_cast<int*>(p->fwd_order) + 2 * g.n_cta + 2 * g.E;
+  return true;
+}
+
 static void attach_bwd_tables(const fm_attn_args* a, AttnKParams* p) {
   OrderGeom g;
   p->dq_sched = p->dkdv_sched = nullptr;
@@ -320,9 +343,11 @@ extern "C" int fm_kernel_status(int* status, int reset) {
   if (rc != FM_OK) return rc;
   rc = bwd_sm100_status(&bw, reset != 0);
   if (rc != FM_OK) return rc;
-  int bp = 0;
+  int bp = 0, fp = 0;
   rc = bwd_sm100_persist_status(&bp, reset != 0);
-  *status = f ? f : (bw ? bw : bp);
+  if (rc != FM_OK) return rc;
+  rc = fwd_sm100_persist_status(&fp, reset != 0);
+  *status = f ? f : (bw ? bw : (bp ? bp : fp));
   return rc;
 }
 

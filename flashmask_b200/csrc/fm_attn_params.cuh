@@ -21,8 +21,8 @@ struct AttnKParams {
   const int32_t* fwd_order; const int32_t* dq_order; const int32_t* dkdv_order;
   // state behind a backward table: [0] next table entry, [1] CTAs that left, [2] 1 when the persistent
   // variant runs on this table, 0 when the one-unit-per-CTA variant does (written by the table builder)
-  int* dq_sched; int* dkdv_sched;
-  int dq_ncta, dkdv_ncta;   // entries of the tables
+  int* dq_sched; int* dkdv_sched; int* fwd_sched;
+  int dq_ncta, dkdv_ncta, fwd_ncta;   // entries of the tables
 };
 
 // CTA coordinates under a launch order: the CTAs of a launch are numbered in

@@ -26,6 +26,16 @@ using namespace sm100;
 
 __device__ int g_fwd_status = 0;
 
+#ifdef FM_TRACE
+// Debug build only: clock stamps at the phase boundaries of CTAs (x < 64, y = 0, z = 0).
+__device__ long long g_fprof[64 * 8];
+#define FPROF(slot) do { if (blockIdx.y == 0 && blockIdx.z == 0 && blockIdx.x < 64) g_fprof[blockIdx.x * 8 + (slot)] = clock64(); } while (0)
+#define FPROF_VAL(slot, v) do { if (blockIdx.y == 0 && blockIdx.z == 0 && blockIdx.x < 64) g_fprof[blockIdx.x * 8 + (slot)] = (v); } while (0)
+#else
+#define FPROF(slot)
+#define FPROF_VAL(slot, v)
+#endif
+
 template <int D>
 struct FwdSm100Cfg {
   static constexpr int BM = 128, BN = 128, NSTAGE = 4, NBND = 2, LIST_MAX = 2048;
@@ -70,6 +80,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int tid = threadIdx.x;
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
   const int lane = tid & 31;
+  if (tid == 0) FPROF(0);
   // descriptor fetches start before anything else: the first loads wait on them
   if (warp == 8 && lane == 0) { tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); }
   const int n_tiles = (p.Sq + 255) / 256;
@@ -140,6 +151,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const uint32_t tmem = (uint32_t)misc[0];
   const int cnt = misc[1];
   WaitCtx wc{misc + 4, global_timer_ns() + 2000000000ull};
+  if (tid == 0) { FPROF(1); FPROF_VAL(7, (long long)cnt); }
   if (cnt == 0) {
     // nothing visible for these 256 rows: write O = 0 and LSE = -inf (sink
     // present: LSE = sink); the Q loads already in flight are awaited and the
@@ -191,97 +203,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (flags) {
         ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_SFULL + s), (uint32_t)n_done & 1u, wc));
         if (!ok) break;
-        tc_fence_after();
-        uint32_t sr[128];
-        tmem_ld32(tS + 0, sr); tmem_ld32(tS + 32, sr + 32); tmem_ld32(tS + 64, sr + 64); tmem_ld32(tS + 96, sr + 96);
-        tc_wait_ld();
-        const uint32_t NEG = 0xff800000u;
-        if (flags & FM_TF_BOUNDS) {
-          const int4* bp = reinterpret_cast<const int4*>(smem + Cfg::OFF_BND + bslot * Cfg::BND_BYTES);
-          if (md.ncols == 1) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int4 v = bp[j];
-              if (row >= v.x) sr[4 * j] = NEG;
-              if (row >= v.y) sr[4 * j + 1] = NEG;
-              if (row >= v.z) sr[4 * j + 2] = NEG;
-              if (row >= v.w) sr[4 * j + 3] = NEG;
-            }
-          } else if (md.ncols == 2 && md.causal) {
-#pragma unroll
-            for (int j = 0; j < 64; ++j) {
-              const int4 v = bp[j];
-              if (row >= v.x && row < v.y) sr[2 * j] = NEG;
-              if (row >= v.z && row < v.w) sr[2 * j + 1] = NEG;
-            }
-          } else if (md.ncols == 2) {
-#pragma unroll
-            for (int j = 0; j < 64; ++j) {
-              const int4 v = bp[j];
-              if (row >= v.x || row < v.y) sr[2 * j] = NEG;
-              if (row >= v.z || row < v.w) sr[2 * j + 1] = NEG;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 128; ++j) {
-              const int4 v = bp[j];
-              if ((row >= v.x && row < v.y) || (row >= v.z && row < v.w)) sr[j] = NEG;
-            }
-          }
-        }
-        if (flags & (FM_TF_CAUSAL | FM_TF_RAGGED)) {
-          const int j0 = (int)(e & 0xFFFFu) * 128;
-          int jmax = p.Sk - 1 - j0;                      // last valid key column of this tile
-          if (md.causal) jmax = min(jmax, row + off - j0);
-#pragma unroll
-          for (int j = 0; j < 128; ++j)
-            if (j > jmax) sr[j] = NEG;
-        }
-        // ---- row maximum, lazy rescale ----
-        float mx0 = neg_inf(), mx1 = neg_inf(), mx2 = neg_inf(), mx3 = neg_inf();
-#pragma unroll
-        for (int j = 0; j < 128; j += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(sr[j])); mx1 = fmaxf(mx1, __uint_as_float(sr[j + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(sr[j + 2])); mx3 = fmaxf(mx3, __uint_as_float(sr[j + 3]));
-        }
-        const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2);
-        const bool need = (m_new - m_run) > 8.0f;
-        float alpha = 1.f;
-        if (need) {
-          alpha = fast_exp2(m_run - m_new);             // m_run == -inf -> 0
-          m_run = m_new;
-          l_run *= alpha;
-        }
-        if (__any_sync(0xffffffffu, need) && n_done > 0) {
-          ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_ODONE + s), (uint32_t)(n_done - 1) & 1u, wc));
-          if (!ok) break;
-          tc_fence_after();
-#pragma unroll
-          for (int c = 0; c < DV / 32; ++c) {
-            uint32_t orr[32];
-            tmem_ld32(tO + 32 * c, orr);
-            tc_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * alpha);
-            tmem_st32(tO + 32 * c, orr);
-          }
-        }
-        // ---- P = exp2(S * scale_log2 - m), bf16 into TMEM ----
-        const float m_use = (m_run == neg_inf()) ? 0.f : m_run;
-        float ls0 = 0.f, ls1 = 0.f;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[32 * c + 2 * j]), scale_log2, -m_use));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[32 * c + 2 * j + 1]), scale_log2, -m_use));
-            ls0 += p0; ls1 += p1;
-            pk[j] = pack2<IS_BF16>(p0, p1);
-          }
-          tmem_st16(tP + 16 * c, pk);
-        }
-        l_run += ls0 + ls1;
+        if (tid == 0 && n_done == 0) FPROF(2);
+#define FM_N_UNIT n_done
+#define FM_N_TOT n_done
+#include "fm_fwd_sm100_tile.inc"
+#undef FM_N_UNIT
+#undef FM_N_TOT
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar(Cfg::B_PFULL + s));
@@ -293,10 +220,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
     }
     // ---- epilogue: O / l -> bf16 -> smem staging -> coalesced stores; LSE ----
+    if (tid == 0) FPROF(3);
     if (ok && n_done > 0) {
       ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_ODONE + s), (uint32_t)(n_done - 1) & 1u, wc));
       tc_fence_after();
     }
+    if (tid == 0) FPROF(4);
     if (ok) {
       const float m_fin = (m_run == neg_inf()) ? 0.f : m_run;
       float l_tot = l_run;
@@ -339,6 +268,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
       }
     }
+    if (tid == 0) FPROF(5);
   } else {
     setmaxnreg_dec<64>();
     if (warp == 8) {
@@ -440,6 +370,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (tid == 0) FPROF(6);
   const bool aborted = misc[4] != 0;
   if (aborted) {
     // give copies and MMAs still in flight a bounded time to land before the
@@ -454,6 +385,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 // ---------------------------------------------------------------------------
 // host
 // ---------------------------------------------------------------------------
+#ifdef FM_TRACE
+extern "C" __attribute__((visibility("default"))) int fm_debug_fprof_read(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_fprof, sizeof(long long) * 64 * 8);
+}
+#endif
+
 namespace sm100 {
 
 EncodeTiledFn get_encode_tiled() {
