@@ -17,6 +17,8 @@
 // maximum grew by more than 2^8 (the rescale is done by the softmax warps
 // themselves).  Every mbarrier wait is bounded: on expiry the CTA raises an
 // abort flag, all roles unwind, TMEM is freed and a status word is set.
+#include <type_traits>
+
 #include "fm_attn_params.cuh"
 #include "fm_sm100.cuh"
 
@@ -319,7 +321,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const uint64_t dq0 = make_sdesc(sQ, 16, 1024);
         const uint64_t dk0 = make_sdesc(sKV, 16, 1024);
         const uint64_t dv0 = make_sdesc(sKV, Cfg::SUB, 1024);
-        auto issue_qk = [&](int s, int i) {
+        auto issue_qk = [&](auto sub, int i) {
+            constexpr int s = decltype(sub)::value;   // compile-time: the per-sub-tile counters stay in registers
           const int k = 2 * i, slot = k % Cfg::NSTAGE;
           ok = ok && mbar_wait(bar(Cfg::B_KVFULL + slot), (uint32_t)(k / Cfg::NSTAGE) & 1u, wc);
           if (ok && !q_ready[s]) { ok = mbar_wait(bar(Cfg::B_QFULL + s), 0u, wc); q_ready[s] = true; }
@@ -331,7 +334,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           umma_ss_x8<(Cfg::SUB >> 4), (Cfg::SUB >> 4)>(dst, da, db, idesc_qk, 0u);
           tc_commit(bar(Cfg::B_SFULL + s));
         };
-        auto issue_pv = [&](int s, int i) {
+        auto issue_pv = [&](auto sub, int i) {
+            constexpr int s = decltype(sub)::value;
           const int k = 2 * i + 1, slot = k % Cfg::NSTAGE;
           ok = ok && mbar_wait(bar(Cfg::B_KVFULL + slot), (uint32_t)(k / Cfg::NSTAGE) & 1u, wc);
           ok = ok && mbar_wait(bar(Cfg::B_PFULL + s), (uint32_t)npv[s] & 1u, wc);
@@ -346,17 +350,17 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         };
         if (cnt > 0) {
           const uint32_t e = list[0];
-          for (int s = 0; s < 2; ++s)
-            if ((e >> (16 + 4 * s)) & 0xFu) issue_qk(s, 0);
+          if ((e >> 16) & 0xFu) issue_qk(std::integral_constant<int, 0>{}, 0);
+          if ((e >> 20) & 0xFu) issue_qk(std::integral_constant<int, 1>{}, 0);
           if (ok) tc_commit(bar(Cfg::B_KVEMPTY + 0));
         }
         for (int i = 0; i < cnt && ok; ++i) {
           const uint32_t e = list[i];
           const uint32_t en = (i + 1 < cnt) ? list[i + 1] : 0u;
-          for (int s = 0; s < 2 && ok; ++s) {
-            if ((e >> (16 + 4 * s)) & 0xFu) issue_pv(s, i);
-            if (ok && ((en >> (16 + 4 * s)) & 0xFu)) issue_qk(s, i + 1);
-          }
+          if ((e >> 16) & 0xFu) issue_pv(std::integral_constant<int, 0>{}, i);
+          if (ok && ((en >> 16) & 0xFu)) issue_qk(std::integral_constant<int, 0>{}, i + 1);
+          if (ok && ((e >> 20) & 0xFu)) issue_pv(std::integral_constant<int, 1>{}, i);
+          if (ok && ((en >> 20) & 0xFu)) issue_qk(std::integral_constant<int, 1>{}, i + 1);
           if (!ok) break;
           tc_commit(bar(Cfg::B_KVEMPTY + (2 * i + 1) % Cfg::NSTAGE));
           if (i + 1 < cnt) tc_commit(bar(Cfg::B_KVEMPTY + (2 * i + 2) % Cfg::NSTAGE));

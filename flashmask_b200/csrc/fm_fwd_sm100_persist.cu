@@ -17,6 +17,8 @@
 // 10 scheduler + list builder, 11 idle.  All waits are bounded.
 #include <algorithm>
 
+#include <type_traits>
+
 #include "fm_attn_params.cuh"
 #include "fm_sm100.cuh"
 
@@ -389,7 +391,8 @@ fwd_sm100_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
           const int cnt_s[2] = {infos[us * 8 + 6], infos[us * 8 + 7]};
           int nqk[2] = {0, 0}, npv[2] = {0, 0};     // per unit
           bool q_ready[2] = {false, false};
-          auto issue_qk = [&](int s, int i) {
+          auto issue_qk = [&](auto sub, int i) {
+            constexpr int s = decltype(sub)::value;   // compile-time: the per-sub-tile counters stay in registers
             const int k = kb + 2 * i, slot = k % Cfg::NSTAGE;
             ok = ok && mbar_wait(bar(Cfg::B_KVFULL + slot), (uint32_t)(k / Cfg::NSTAGE) & 1u, wc);
             if (ok && !q_ready[s]) { ok = mbar_wait(bar(Cfg::B_QFULL + s), (uint32_t)j & 1u, wc); q_ready[s] = true; }
@@ -404,7 +407,8 @@ fwd_sm100_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
             // after the last S = Q K^T of the unit (both sub-tiles) the Q tiles may be replaced
             if (nqk[0] == cnt_s[0] && nqk[1] == cnt_s[1]) tc_commit(bar(Cfg::B_QFREE));
           };
-          auto issue_pv = [&](int s, int i) {
+          auto issue_pv = [&](auto sub, int i) {
+            constexpr int s = decltype(sub)::value;
             const int k = kb + 2 * i + 1, slot = k % Cfg::NSTAGE;
             ok = ok && mbar_wait(bar(Cfg::B_KVFULL + slot), (uint32_t)(k / Cfg::NSTAGE) & 1u, wc);
             ok = ok && mbar_wait(bar(Cfg::B_PFULL + s), (uint32_t)npv_tot[s] & 1u, wc);
@@ -426,17 +430,17 @@ fwd_sm100_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
           }
           {
             const uint32_t e = list[0];
-            for (int s = 0; s < 2; ++s)
-              if ((e >> (16 + 4 * s)) & 0xFu) issue_qk(s, 0);
+            if ((e >> 16) & 0xFu) issue_qk(std::integral_constant<int, 0>{}, 0);
+            if ((e >> 20) & 0xFu) issue_qk(std::integral_constant<int, 1>{}, 0);
             if (ok) tc_commit(bar(Cfg::B_KVEMPTY + (kb + 0) % Cfg::NSTAGE));
           }
           for (int i = 0; i < cnt && ok; ++i) {
             const uint32_t e = list[i];
             const uint32_t en = (i + 1 < cnt) ? list[i + 1] : 0u;
-            for (int s = 0; s < 2 && ok; ++s) {
-              if ((e >> (16 + 4 * s)) & 0xFu) issue_pv(s, i);
-              if (ok && ((en >> (16 + 4 * s)) & 0xFu)) issue_qk(s, i + 1);
-            }
+            if ((e >> 16) & 0xFu) issue_pv(std::integral_constant<int, 0>{}, i);
+            if (ok && ((en >> 16) & 0xFu)) issue_qk(std::integral_constant<int, 0>{}, i + 1);
+            if (ok && ((e >> 20) & 0xFu)) issue_pv(std::integral_constant<int, 1>{}, i);
+            if (ok && ((en >> 20) & 0xFu)) issue_qk(std::integral_constant<int, 1>{}, i + 1);
             if (!ok) break;
             tc_commit(bar(Cfg::B_KVEMPTY + (kb + 2 * i + 1) % Cfg::NSTAGE));
             if (i + 1 < cnt) tc_commit(bar(Cfg::B_KVEMPTY + (kb + 2 * i + 2) % Cfg::NSTAGE));
