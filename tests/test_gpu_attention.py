@@ -198,6 +198,7 @@ def test_launch_order_changes_no_bit(kind, mask_b, hm, persist, monkeypatch):
     persistent backward variant only changes which CTA runs which unit: results are bitwise
     those of the index order, for every mask batch / head broadcast and both backward variants."""
     monkeypatch.setenv("FLASHMASK_B200_PERSIST", persist)
+    monkeypatch.setenv("FLASHMASK_B200_FWD_PERSIST", persist)   # the persistent forward is opt-in
     B, S, Hq, Hkv = 2, 1024, 8, 2
     idx_np, causal = _mask(kind, B, S, S, 33)
     idx_np = np.ascontiguousarray(idx_np[:mask_b]).copy()
@@ -206,7 +207,6 @@ def test_launch_order_changes_no_bit(kind, mask_b, hm, persist, monkeypatch):
         idx_np = np.concatenate([idx_np, other], axis=1)
     q, k, v, do, s = make_inputs(B, S, S, Hq, Hkv, 128, 128, 33, sink=True)
     idx = torch.from_numpy(idx_np).cuda()
-    monkeypatch.setenv("FLASHMASK_B200_ORDER_FORCE", "1")   # all three kernels, whatever the size
     monkeypatch.setenv("FLASHMASK_B200_ORDER", "0")
     a = run_product(q.cuda(), k.cuda(), v.cuda(), do.cuda(), idx, causal, s, deterministic=True)
     monkeypatch.setenv("FLASHMASK_B200_ORDER", "1")

@@ -106,7 +106,6 @@ def test_launch_order_bit_exact(Sq, Sk, mask_b, hm, monkeypatch):
     import ctypes as C
     from flashmask_b200 import _lib
     lib = _lib.load()
-    monkeypatch.setenv("FLASHMASK_B200_ORDER_FORCE", "1")   # also the orders the size policy would skip
     B, Hq, Hkv = 2, 4, 2
     for name, (idx_np, causal) in _masks(mask_b * hm, Sq, Sk, Sq + 3 * Sk):
         idx_np = idx_np.copy()
