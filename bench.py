@@ -437,6 +437,12 @@ def main():
             "gpu_launches": launches_per_step() * args.steps, "roofline": roofline,
             "frac_of_peak_fwd_bwd": value / world / peak_tf,
             "tokens_per_s": world * w.B * w.Sq / (ms_step * 1e-3)}
+    if w.Sq <= 16384:
+        # the reference benchmark's accounting: every 128x128 block with one unmasked element counts in full
+        dens = W.block_density(w.idx, w.B, w.Sq, w.Sk, w.causal)
+        blk_flops = 2.0 * w.B * w.Hq * w.Sq * w.Sk * dens * (4 * w.d + 3 * w.dv)
+        line["block_density_convention"] = {"density": dens, "value": world * blk_flops / (ms_step * 1e-3) / 1e12,
+                                            "unit": UNIT}
     if world == 1 and not args.no_e2e and args.workload is None:
         # the context-parallel workload on this one GPU: the N=1 point of the 128K scaling series
         wc = W.make_workload("cp_causal_doc_128k")
