@@ -177,7 +177,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
   if (warp < 8) {
     // =========================== softmax warpgroups ===========================
-    setmaxnreg_inc<200>();
+    setmaxnreg_inc<216>();
     const int s = warp >> 2;
     const int r = tid & 127;                   // row inside the sub-tile == TMEM lane
     const int row = ms + 128 * s + r;

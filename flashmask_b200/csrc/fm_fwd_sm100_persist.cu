@@ -113,7 +113,7 @@ fwd_sm100_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
 
   if (warp < 8) {
     // =========================== softmax warpgroups ===========================
-    setmaxnreg_inc<200>();
+    setmaxnreg_inc<216>();
     const int s = warp >> 2;
     const int r = tid & 127;                   // row inside the sub-tile == TMEM lane
     const uint32_t lane_field = (uint32_t)((warp & 3) * 32) << 16;
