@@ -46,10 +46,10 @@ int bounded_wait_selftest_launch(uint64_t budget_ns, cudaStream_t s);
 
 static inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
-// Kernel variant of the forward for (d, dv): the tcgen05 kernel covers
-// d = dv = 128; FLASHMASK_B200_FWD=mma forces the warp-MMA variant (A/B runs).
+// Kernel variant of the forward for (d, dv): the tcgen05 kernels cover head dims up to
+// 128 (multiples of 8); FLASHMASK_B200_FWD=mma forces the warp-MMA variant (A/B runs).
 static bool fwd_uses_sm100(int d, int dv) {
-  if (!(d == 128 && dv == 128)) return false;
+  if (d > 128 || dv > 128 || d % 8 || dv % 8) return false;
   const char* e = getenv("FLASHMASK_B200_FWD");
   return !(e && strcmp(e, "mma") == 0);
 }
@@ -124,7 +124,7 @@ extern "C" const char* fm_version(void) { return "flashmask_b200 0.1.0 sm_100a";
 extern "C" const char* fm_last_error(void) { return g_err; }
 
 static bool bwd_uses_sm100(int d, int dv) {
-  if (!(d == 128 && dv == 128)) return false;
+  if (d > 128 || dv > 128 || d % 8 || dv % 8) return false;
   const char* e = getenv("FLASHMASK_B200_BWD");
   return !(e && strcmp(e, "mma") == 0);
 }

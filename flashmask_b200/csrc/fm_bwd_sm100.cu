@@ -1,5 +1,7 @@
 // Backward attention on the 5th-generation tensor cores (tcgen05 / UMMA) for
-// d = dv = 128, as two kernels that share one pipeline skeleton:
+// head dims up to 128 (smaller ones, multiples of 8, are computed at width 128:
+// the TMA loads fill the columns past the end of a head with zeros and the
+// epilogues leave them unwritten), as two kernels that share one pipeline skeleton:
 //
 //   MODE_DKDV  one CTA per (128-key tile, kv head, batch).  K and V stay in
 //              shared memory; 64-row halves of Q and dO stream through a ring
@@ -83,7 +85,10 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
                : "memory");
 }
 
-template <int MODE, bool IS_BF16>
+// D: width the head dims are computed at (64 when both fit, else 128).  The 64-column variant
+// keeps the shared-memory layout of the 128-column one and simply leaves the second 64-column
+// sub-tile of every operand unloaded and unread: half the copies, half the tensor work.
+template <int MODE, bool IS_BF16, int D>
 __global__ void __launch_bounds__(384, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_constant__ CUtensorMap tm_stat2,
                  const __grid_constant__ CUtensorMap tm_str1, const __grid_constant__ CUtensorMap tm_str2,
@@ -135,10 +140,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
     mbar_init(bar(Cfg::B_ACC), 1);
     fence_mbar_init();
     // the stationary tiles are requested right away: the loads overlap with the list build
-    mbar_arrive_expect_tx(bar(Cfg::B_STAT), 2 * Cfg::TILE_BYTES);
+    mbar_arrive_expect_tx(bar(Cfg::B_STAT), 2 * Cfg::TILE_BYTES * D / 128);
     {
       const int hs = (MODE == MODE_DKDV) ? hk : hq0;
-      for (int dc = 0; dc < 2; ++dc) {
+      for (int dc = 0; dc < D / 64; ++dc) {
         tma_load_4d(sStat + dc * Cfg::SUB128, &tm_stat1, bar(Cfg::B_STAT), dc * 64, hs, row0, b);
         tma_load_4d(sStat + Cfg::TILE_BYTES + dc * Cfg::SUB128, &tm_stat2, bar(Cfg::B_STAT), dc * 64, hs, row0, b);
       }
@@ -213,15 +218,16 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
       for (int x = tid; x < 128 * 16; x += Cfg::NTHREADS) {
         const int rr = x >> 4, cc = x & 15;
         if (row0 + rr < p.Sk) {
-          *reinterpret_cast<uint4*>(gk + (int64_t)rr * p.dk_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
-          *reinterpret_cast<uint4*>(gv + (int64_t)rr * p.dv_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
+          if (cc * 8 < p.d) *reinterpret_cast<uint4*>(gk + (int64_t)rr * p.dk_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
+          if (cc * 8 < p.dv_dim) *reinterpret_cast<uint4*>(gv + (int64_t)rr * p.dv_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
         }
       }
     } else {
       uint16_t* gq = reinterpret_cast<uint16_t*>(p.dq) + b * p.dq_b + (int64_t)row0 * p.dq_s + hq0 * p.dq_h;
       for (int x = tid; x < 128 * 16; x += Cfg::NTHREADS) {
         const int rr = x >> 4, cc = x & 15;
-        if (row0 + rr < p.Sq) *reinterpret_cast<uint4*>(gq + (int64_t)rr * p.dq_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
+        if (row0 + rr < p.Sq && cc * 8 < p.d)
+          *reinterpret_cast<uint4*>(gq + (int64_t)rr * p.dq_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
       }
     }
     return;
@@ -309,7 +315,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
         const float mul = pz == 0 ? p.scale : 1.f;
         uint8_t* stage = smem + Cfg::OFF_STAT + pz * Cfg::TILE_BYTES;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < D / 32; ++c) {
           uint32_t orr[32];
           if (K_items > 0) { tmem_ld32(tA + 32 * c, orr); tc_wait_ld(); }
           else {
@@ -332,20 +338,21 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
             ? reinterpret_cast<uint16_t*>(p.dk) + b * p.dk_b + (int64_t)row0 * p.dk_s + hk * p.dk_h
             : reinterpret_cast<uint16_t*>(p.dv) + b * p.dv_b + (int64_t)row0 * p.dv_s + hk * p.dv_h;
         const int64_t ld = pz == 0 ? p.dk_s : p.dv_s;
+        const int width = pz == 0 ? p.d : p.dv_dim;   // columns past the head dim hold products of zero fill
         const int wrow = (warp & 3) * 32;
 #pragma unroll 4
-        for (int x = lane; x < 32 * 16; x += 32) {
-          const int rr = wrow + (x >> 4), cc = x & 15;
-          if (row0 + rr < p.Sk)
+        for (int x = lane; x < 32 * (D / 8); x += 32) {
+          const int rr = wrow + x / (D / 8), cc = x % (D / 8);
+          if (row0 + rr < p.Sk && cc * 8 < width)
             *reinterpret_cast<uint4*>(gout + (int64_t)rr * ld + cc * 8) =
                 *reinterpret_cast<const uint4*>(stage + rr * 256 + ((cc ^ (rr & 15)) << 4));
         }
       } else {
-        // both warpgroups: dQ columns [64 pz, 64 pz + 64), staged in the Q tile
-        const uint32_t tA = tmem + lane_field + C_ACC1 + 64u * pz;
+        // both warpgroups: dQ columns [D/2 pz, D/2 pz + D/2), staged in the Q tile
+        const uint32_t tA = tmem + lane_field + C_ACC1 + (uint32_t)(D / 2) * pz;
         uint8_t* stage = smem + Cfg::OFF_STAT;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < D / 64; ++c) {
           uint32_t orr[32];
           if (K_items > 0) { tmem_ld32(tA + 32 * c, orr); tc_wait_ld(); }
           else {
@@ -359,7 +366,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
             v.y = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 2]) * p.scale, __uint_as_float(orr[8 * q4 + 3]) * p.scale);
             v.z = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 4]) * p.scale, __uint_as_float(orr[8 * q4 + 5]) * p.scale);
             v.w = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 6]) * p.scale, __uint_as_float(orr[8 * q4 + 7]) * p.scale);
-            const int chunk = 8 * pz + 4 * c + q4;
+            const int chunk = (D / 16) * pz + 4 * c + q4;
             *reinterpret_cast<uint4*>(stage + r * 256 + ((chunk ^ (r & 15)) << 4)) = v;
           }
         }
@@ -367,9 +374,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
         uint16_t* gout = reinterpret_cast<uint16_t*>(p.dq) + b * p.dq_b + (int64_t)row0 * p.dq_s + hq0 * p.dq_h;
         const int wrow = (warp & 3) * 32;
 #pragma unroll 4
-        for (int x = lane; x < 32 * 8; x += 32) {
-          const int rr = wrow + (x >> 3), cc = 8 * pz + (x & 7);
-          if (row0 + rr < p.Sq)
+        for (int x = lane; x < 32 * (D / 16); x += 32) {
+          const int rr = wrow + x / (D / 16), cc = (D / 16) * pz + x % (D / 16);
+          if (row0 + rr < p.Sq && cc * 8 < p.d)
             *reinterpret_cast<uint4*>(gout + (int64_t)rr * p.dq_s + cc * 8) =
                 *reinterpret_cast<const uint4*>(stage + rr * 256 + ((cc ^ (rr & 15)) << 4));
         }
@@ -398,8 +405,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
         if (elect_one()) {
           const uint32_t dst = sRing + slot * Cfg::SLOT_BYTES;
           const uint32_t fb = bar(Cfg::B_RFULL + slot);
-          mbar_arrive_expect_tx(fb, Cfg::SLOT_BYTES + (MODE == MODE_DKDV ? 512 : 0));
-          for (int dc = 0; dc < 2; ++dc) {
+          mbar_arrive_expect_tx(fb, Cfg::SLOT_BYTES * D / 128 + (MODE == MODE_DKDV ? 512 : 0));
+          for (int dc = 0; dc < D / 64; ++dc) {
             tma_load_4d(dst + dc * Cfg::SUB64, &tm_str1, fb, dc * 64, hstr, idx * 64, b);
             tma_load_4d(dst + Cfg::HALF_BYTES + dc * Cfg::SUB64, &tm_str2, fb, dc * 64, hstr, idx * 64, b);
           }
@@ -424,7 +431,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
       // =========================== UMMA issuer ===========================
       if (K_items > 0 && elect_one()) {
         constexpr uint32_t idesc_g = make_idesc(IS_BF16, 128, 64, 0, 0);
-        constexpr uint32_t idesc_acc = make_idesc(IS_BF16, 128, 128, 0, 1);
+        constexpr uint32_t idesc_acc = make_idesc(IS_BF16, 128, D, 0, 1);
         bool ok = mbar_wait(bar(Cfg::B_STAT), 0u, wc);
         PROF(2);
         // descriptors are built once; per MMA only a constant is added to the
@@ -443,8 +450,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
           TRACE(1, 21, k);                    // ring slot full
           tc_fence_after();
           const uint64_t db1 = dRk + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));
-          umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(tmem + C_G1 + 64u * pz, dA1, db1, idesc_g, 0u);
-
+          if constexpr (D == 128) umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(tmem + C_G1 + 64u * pz, dA1, db1, idesc_g, 0u);
+          else umma_ss_x4(tmem + C_G1 + 64u * pz, dA1, db1, idesc_g, 0u);
           TRACE(1, 22, k);                    // G issued
         };
         // part 2: the second score GEMM (dP or dP^T) follows the accumulation MMAs of the
@@ -454,7 +461,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
           {
             const int slot = k % Cfg::NSLOT, pz = k & 1;
             const uint64_t db2 = dRk + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4) + (Cfg::HALF_BYTES >> 4));
-            umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(tmem + C_G2 + 64u * pz, dA2, db2, idesc_g, 0u);
+            if constexpr (D == 128) umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(tmem + C_G2 + 64u * pz, dA2, db2, idesc_g, 0u);
+            else umma_ss_x4(tmem + C_G2 + 64u * pz, dA2, db2, idesc_g, 0u);
             tc_commit(bar(Cfg::B_GFULL + pz));
           }
         };
@@ -514,12 +522,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
 // host
 // ---------------------------------------------------------------------------
 bool bwd_sm100_supported(const fm_attn_args* a) {
-  if (!(a->d == 128 && a->dv == 128)) return false;
+  if (a->d > 128 || a->dv > 128 || a->d % 8 || a->dv % 8) return false;
   if (((uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v | (uintptr_t)a->d_o) & 15) return false;
   return true;
 }
 
-template <bool IS_BF16>
+template <bool IS_BF16, int D>
 static int launch_bwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
   using Cfg = BwdSm100Cfg;
   FM_REQUIRE((a->Sq + 63) / 64 <= Cfg::LIST_MAX && (a->Sk + 63) / 64 <= Cfg::LIST_MAX, FM_ERR_UNSUPPORTED,
@@ -538,8 +546,8 @@ static int launch_bwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStr
   FM_TMAP(k64, a->k, a->Sk, a->Hkv, a->d, a->k_stride, 64)
   FM_TMAP(v64, a->v, a->Sk, a->Hkv, a->dv, a->v_stride, 64)
 #undef FM_TMAP
-  auto k1 = bwd_sm100_kernel<MODE_DKDV, IS_BF16>;
-  auto k2 = bwd_sm100_kernel<MODE_DQ, IS_BF16>;
+  auto k1 = bwd_sm100_kernel<MODE_DKDV, IS_BF16, D>;
+  auto k2 = bwd_sm100_kernel<MODE_DQ, IS_BF16, D>;
   FM_CUDA_TRY(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
   FM_CUDA_TRY(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
   k1<<<dim3((p.Sk + 127) / 128, p.Hkv, p.B), Cfg::NTHREADS, Cfg::SMEM, s>>>(k128, v128, q64, do64, p);
@@ -550,7 +558,9 @@ static int launch_bwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStr
 }
 
 int bwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
-  return a->dtype == FM_DTYPE_BF16 ? launch_bwd_sm100<true>(p, a, s) : launch_bwd_sm100<false>(p, a, s);
+  const bool bf = a->dtype == FM_DTYPE_BF16;
+  if (a->d <= 64 && a->dv <= 64) return bf ? launch_bwd_sm100<true, 64>(p, a, s) : launch_bwd_sm100<false, 64>(p, a, s);
+  return bf ? launch_bwd_sm100<true, 128>(p, a, s) : launch_bwd_sm100<false, 128>(p, a, s);
 }
 
 #ifdef FM_TRACE

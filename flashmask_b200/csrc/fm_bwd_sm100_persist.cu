@@ -108,7 +108,9 @@ __device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* tmap, int c0,
 // the scheduler warp already fetches the next one, builds its work list and prefetches its
 // stationary tile into L2, so that entry, list build and most of the first loads disappear
 // from the critical path of short units.
-template <int MODE, bool IS_BF16>
+// D: width the head dims are computed at (64 when both fit, else 128); the 64-column variant keeps
+// the shared-memory layout and leaves the second 64-column sub-tile of every operand unloaded.
+template <int MODE, bool IS_BF16, int D>
 __global__ void __launch_bounds__(512, 1)
 bwd_sm100_persist_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_constant__ CUtensorMap tm_stat2,
                  const __grid_constant__ CUtensorMap tm_str1, const __grid_constant__ CUtensorMap tm_str2,
@@ -312,15 +314,16 @@ bwd_sm100_persist_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __g
           for (int x = tid; x < 128 * 16; x += 256) {
             const int rr = x >> 4, cc = x & 15;
             if (row0 + rr < p.Sk) {
-              *reinterpret_cast<uint4*>(gk + (int64_t)rr * p.dk_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
-              *reinterpret_cast<uint4*>(gv + (int64_t)rr * p.dv_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
+              if (cc * 8 < p.d) *reinterpret_cast<uint4*>(gk + (int64_t)rr * p.dk_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
+              if (cc * 8 < p.dv_dim) *reinterpret_cast<uint4*>(gv + (int64_t)rr * p.dv_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
             }
           }
         } else {
           uint16_t* gq = reinterpret_cast<uint16_t*>(p.dq) + b * p.dq_b + (int64_t)row0 * p.dq_s + hq0 * p.dq_h;
           for (int x = tid; x < 128 * 16; x += 256) {
             const int rr = x >> 4, cc = x & 15;
-            if (row0 + rr < p.Sq) *reinterpret_cast<uint4*>(gq + (int64_t)rr * p.dq_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
+            if (row0 + rr < p.Sq && cc * 8 < p.d)
+              *reinterpret_cast<uint4*>(gq + (int64_t)rr * p.dq_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
           }
         }
         __syncwarp();
@@ -408,8 +411,8 @@ bwd_sm100_persist_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __g
         if (!ok) break;
       }
       if (elect_one()) {
-        mbar_arrive_expect_tx(bar(Cfg::B_STAT), 2 * Cfg::TILE_BYTES);
-        for (int dc = 0; dc < 2; ++dc) {
+        mbar_arrive_expect_tx(bar(Cfg::B_STAT), 2 * Cfg::TILE_BYTES * D / 128);
+        for (int dc = 0; dc < D / 64; ++dc) {
           tma_load_4d(sStat + dc * Cfg::SUB128, &tm_stat1, bar(Cfg::B_STAT), dc * 64, head, row0, b);
           tma_load_4d(sStat + Cfg::TILE_BYTES + dc * Cfg::SUB128, &tm_stat2, bar(Cfg::B_STAT), dc * 64, head, row0, b);
         }
@@ -441,8 +444,8 @@ bwd_sm100_persist_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __g
         if (elect_one()) {
           const uint32_t dst = sRing + slot * Cfg::SLOT_BYTES;
           const uint32_t fb = bar(Cfg::B_RFULL + slot);
-          mbar_arrive_expect_tx(fb, Cfg::SLOT_BYTES + (MODE == MODE_DKDV ? 512 : 0));
-          for (int dc = 0; dc < 2; ++dc) {
+          mbar_arrive_expect_tx(fb, Cfg::SLOT_BYTES * D / 128 + (MODE == MODE_DKDV ? 512 : 0));
+          for (int dc = 0; dc < D / 64; ++dc) {
             tma_load_4d(dst + dc * Cfg::SUB64, &tm_str1, fb, dc * 64, hstr, idx * 64, b);
             tma_load_4d(dst + Cfg::HALF_BYTES + dc * Cfg::SUB64, &tm_str2, fb, dc * 64, hstr, idx * 64, b);
           }
@@ -472,7 +475,7 @@ bwd_sm100_persist_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __g
     // =========================== UMMA issuer ===========================
     if (elect_one()) {
       constexpr uint32_t idesc_g = make_idesc(IS_BF16, 128, 64, 0, 0);
-      constexpr uint32_t idesc_acc = make_idesc(IS_BF16, 128, 128, 0, 1);
+      constexpr uint32_t idesc_acc = make_idesc(IS_BF16, 128, D, 0, 1);
       // descriptors are built once; per MMA only a constant is added to the
       // 14-bit address field (all smem offsets are multiples of 16 bytes)
       const uint64_t dA1 = make_sdesc(sStat, 16, 1024);
@@ -492,7 +495,8 @@ bwd_sm100_persist_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __g
         TRACE(1, 21, kk);                   // ring slot full
         tc_fence_after();
         const uint64_t db1 = dRk + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));
-        umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(tmem + C_G1 + 64u * pz, dA1, db1, idesc_g, 0u);
+        if constexpr (D == 128) umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(tmem + C_G1 + 64u * pz, dA1, db1, idesc_g, 0u);
+        else umma_ss_x4(tmem + C_G1 + 64u * pz, dA1, db1, idesc_g, 0u);
         TRACE(1, 22, kk);                   // G issued
       };
       // part 2: the second score GEMM (dP or dP^T) follows the accumulation MMAs of item kk-2
@@ -500,7 +504,8 @@ bwd_sm100_persist_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __g
       auto issue_g_late = [&](int kk) {
         const int slot = kk % Cfg::NSLOT, pz = kk & 1;
         const uint64_t db2 = dRk + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4) + (Cfg::HALF_BYTES >> 4));
-        umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(tmem + C_G2 + 64u * pz, dA2, db2, idesc_g, 0u);
+        if constexpr (D == 128) umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(tmem + C_G2 + 64u * pz, dA2, db2, idesc_g, 0u);
+        else umma_ss_x4(tmem + C_G2 + 64u * pz, dA2, db2, idesc_g, 0u);
         tc_commit(bar(Cfg::B_GFULL + pz));
       };
       for (int j = 0; ok; ++j) {
@@ -604,6 +609,7 @@ bwd_sm100_persist_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __g
         // DKDV: o = 0 dV, o = 1 dK (scaled); DQ: dQ (scaled)
         const uint32_t tA = tmem + lane_field + ((MODE == MODE_DKDV && o == 0) ? C_ACC1 : C_ACC2);
         const float mul = (MODE == MODE_DKDV && o == 0) ? 1.f : p.scale;
+        const int width = (MODE == MODE_DKDV && o == 0) ? p.dv_dim : p.d;   // head dims below 128 end here
         uint16_t* gbase;
         int64_t ld;
         if (MODE == MODE_DKDV) {
@@ -615,11 +621,11 @@ bwd_sm100_persist_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __g
           ld = p.dq_s;
         }
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < D / 32; ++c) {
           uint32_t acc[32];
           tmem_ld32(tA + 32 * c, acc);
           tc_wait_ld();
-          if (o == N_OUT - 1 && c == 3) {
+          if (o == N_OUT - 1 && c == D / 32 - 1) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(Cfg::B_ACCFREE));   // the next unit may overwrite the accumulators
@@ -638,7 +644,7 @@ bwd_sm100_persist_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __g
           for (int i = 0; i < 4; ++i) {
             const int rr = 8 * i + (lane >> 2), piece = lane & 3;
             const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 64 + ((piece ^ ((rr >> 1) & 3)) << 4));
-            if (rbase + rr < rlimit)
+            if (rbase + rr < rlimit && 32 * c + 8 * piece < width)
               *reinterpret_cast<uint4*>(gbase + (int64_t)(rbase + rr) * ld + 32 * c + 8 * piece) = v;
           }
           __syncwarp();
@@ -671,7 +677,7 @@ bwd_sm100_persist_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __g
 // ---------------------------------------------------------------------------
 // host
 // ---------------------------------------------------------------------------
-template <bool IS_BF16>
+template <bool IS_BF16, int D>
 static int launch_bwd_sm100_persist(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
   using Cfg = BwdPersistCfg;
   FM_REQUIRE((a->Sq + 63) / 64 <= Cfg::LIST_MAX && (a->Sk + 63) / 64 <= Cfg::LIST_MAX, FM_ERR_UNSUPPORTED,
@@ -690,8 +696,8 @@ static int launch_bwd_sm100_persist(const AttnKParams& p, const fm_attn_args* a,
   FM_TMAP(k64, a->k, a->Sk, a->Hkv, a->d, a->k_stride, 64)
   FM_TMAP(v64, a->v, a->Sk, a->Hkv, a->dv, a->v_stride, 64)
 #undef FM_TMAP
-  auto k1 = bwd_sm100_persist_kernel<MODE_DKDV, IS_BF16>;
-  auto k2 = bwd_sm100_persist_kernel<MODE_DQ, IS_BF16>;
+  auto k1 = bwd_sm100_persist_kernel<MODE_DKDV, IS_BF16, D>;
+  auto k2 = bwd_sm100_persist_kernel<MODE_DQ, IS_BF16, D>;
   FM_CUDA_TRY(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
   FM_CUDA_TRY(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
   // with a launch table: one persistent CTA per SM (fewer when the table is shorter)
@@ -708,7 +714,10 @@ static int launch_bwd_sm100_persist(const AttnKParams& p, const fm_attn_args* a,
 }
 
 int bwd_sm100_persist_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
-  return a->dtype == FM_DTYPE_BF16 ? launch_bwd_sm100_persist<true>(p, a, s) : launch_bwd_sm100_persist<false>(p, a, s);
+  const bool bf = a->dtype == FM_DTYPE_BF16;
+  if (a->d <= 64 && a->dv <= 64)
+    return bf ? launch_bwd_sm100_persist<true, 64>(p, a, s) : launch_bwd_sm100_persist<false, 64>(p, a, s);
+  return bf ? launch_bwd_sm100_persist<true, 128>(p, a, s) : launch_bwd_sm100_persist<false, 128>(p, a, s);
 }
 
 #ifdef FM_TRACE

@@ -1,5 +1,7 @@
 // Forward attention on the 5th-generation tensor cores (tcgen05 / UMMA) for
-// d = dv = 128.
+// head dims up to 128: a 64-column and a 128-column variant; smaller head dims
+// (multiples of 8) run in the next variant up, the TMA loads filling the
+// columns past the end of a head with zeros.
 //
 // One CTA owns 256 query rows of one (batch, q head) as two 128-row sub-tiles
 // that share every K/V tile.  Warp roles:
@@ -11,7 +13,7 @@
 //               O_s += P_s V with P_s read from TMEM; owns the TMEM allocation
 //   warp 10     builds the list of surviving K tiles with per-sub-tile flags
 //   warp 11     idle
-// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512);
+// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D);
 // P_s (bf16, 64 columns) overlays the upper half of S_s.
 // Online softmax keeps a stale running maximum and only rescales O when the
 // maximum grew by more than 2^8 (the rescale is done by the softmax warps
@@ -40,7 +42,8 @@ __device__ long long g_fprof[64 * 8];
 
 template <int D>
 struct FwdSm100Cfg {
-  static constexpr int BM = 128, BN = 128, NSTAGE = 4, NBND = 2, LIST_MAX = 2048;
+  // the 64-column variant doubles the ring depth: its slots are half as large
+  static constexpr int BM = 128, BN = 128, NSTAGE = (D == 64 ? 8 : 4), NBND = 2, LIST_MAX = 2048;
   static constexpr int NTHREADS = 384;
   static constexpr int SUB = 128 * 128;                 // bytes of a 128-row x 64-col bf16 sub-tile
   static constexpr int Q_BYTES = BM * D * 2;
@@ -57,7 +60,9 @@ struct FwdSm100Cfg {
   static constexpr int B_QFULL = 0, B_KVFULL = 2, B_KVEMPTY = 2 + NSTAGE, B_SFULL = 2 + 2 * NSTAGE,
                        B_PFULL = B_SFULL + 2, B_ODONE = B_PFULL + 2, B_BNDFULL = B_ODONE + 2,
                        B_BNDEMPTY = B_BNDFULL + NBND, B_COUNT = B_BNDEMPTY + NBND;
+  static_assert(D == 64 || D == 128, "head-dim variants");
   static_assert(B_COUNT <= 32, "barrier storage");
+  static_assert(NSTAGE * SLOT_BYTES >= LIST_MAX * 8 * 4, "the ring stages the reductions of the list build");
   static_assert(SMEM > 120 * 1024, "one CTA per SM is assumed by the 512-column TMEM allocation");
 };
 
@@ -166,7 +171,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     uint16_t* go = reinterpret_cast<uint16_t*>(p.o) + b * p.o_b + (int64_t)ms * p.o_s + hq * p.o_h;
     for (int x = tid; x < 256 * (DV / 8); x += Cfg::NTHREADS) {
       const int rr = x / (DV / 8), cc = x % (DV / 8);
-      if (ms + rr < p.Sq) *reinterpret_cast<uint4*>(go + (int64_t)rr * p.o_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
+      if (ms + rr < p.Sq && cc * 8 < p.dv_dim)
+        *reinterpret_cast<uint4*>(go + (int64_t)rr * p.o_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
     }
     const float empty_lse = p.sink ? p.sink[hq] : neg_inf();
     for (int rr = tid; rr < 256; rr += Cfg::NTHREADS)
@@ -264,7 +270,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll 4
       for (int idx = lane; idx < 32 * CH; idx += 32) {
         const int rr = wrow + idx / CH, cc = idx % CH;
-        if (ms + 128 * s + rr < p.Sq) {
+        if (ms + 128 * s + rr < p.Sq && cc * 8 < p.dv_dim) {
           const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * (DV * 2) + ((cc ^ (rr & (CH - 1))) << 4));
           *reinterpret_cast<uint4*>(go + (int64_t)rr * p.o_s + cc * 8) = v;
         }
@@ -331,7 +337,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           const uint64_t da = dq0 + (uint64_t)(s * (Cfg::Q_BYTES >> 4));
           const uint64_t db = dk0 + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));
           const uint32_t dst = tmem + 128u * s;
-          umma_ss_x8<(Cfg::SUB >> 4), (Cfg::SUB >> 4)>(dst, da, db, idesc_qk, 0u);
+          if constexpr (D == 128) umma_ss_x8<(Cfg::SUB >> 4), (Cfg::SUB >> 4)>(dst, da, db, idesc_qk, 0u);
+          else umma_ss_x4(dst, da, db, idesc_qk, 0u);
           tc_commit(bar(Cfg::B_SFULL + s));
         };
         auto issue_pv = [&](auto sub, int i) {
@@ -454,7 +461,7 @@ int bounded_wait_selftest_launch(uint64_t budget_ns, cudaStream_t s) {
 }
 
 bool fwd_sm100_supported(const fm_attn_args* a) {
-  if (!(a->d == 128 && a->dv == 128)) return false;
+  if (a->d > 128 || a->dv > 128 || a->d % 8 || a->dv % 8) return false;
   if (((uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v) & 15) return false;
   return true;
 }
@@ -479,6 +486,7 @@ static int launch_fwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStr
 
 int fwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
   const bool bf = a->dtype == FM_DTYPE_BF16;
+  if (a->d <= 64 && a->dv <= 64) return bf ? launch_fwd_sm100<64, true>(p, a, s) : launch_fwd_sm100<64, false>(p, a, s);
   return bf ? launch_fwd_sm100<128, true>(p, a, s) : launch_fwd_sm100<128, false>(p, a, s);
 }
 

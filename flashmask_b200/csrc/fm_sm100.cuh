@@ -216,6 +216,24 @@ __device__ __forceinline__ void umma_ts_xn(uint32_t d_tmem, uint32_t a_tmem, uin
   }
 }
 
+// Four k-steps (K = 64 elements, one 64-column sub-tile per operand) of the same.
+__device__ __forceinline__ void umma_ss_x4(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc,
+                                           uint32_t acc_first) {
+  asm volatile(
+      "{\n\t.reg .pred p, pt;\n\t.reg .b64 ta, tb;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "add.s64 ta, %1, 2;  add.s64 tb, %2, 2;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], ta, tb, %3, pt;\n\t"
+      "add.s64 ta, %1, 4;  add.s64 tb, %2, 4;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], ta, tb, %3, pt;\n\t"
+      "add.s64 ta, %1, 6;  add.s64 tb, %2, 6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], ta, tb, %3, pt;\n\t}"
+      ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(acc_first)
+      : "memory");
+}
+
 // 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread
 // (thread t of warp w reads TMEM lane 32*(w%4)+t).
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {

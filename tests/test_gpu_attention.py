@@ -126,6 +126,22 @@ def test_head_dims(kind, d, dv, Hq, Hkv):
     _run(kind, 1, 320, 320, Hq, Hkv, d, dv, sink=True, seed=5)
 
 
+@pytest.mark.parametrize("kind", MASKS)
+def test_masks_d64(kind, fwd_variant):
+    """Every mask family through the 64-column variants: GQA, rows long enough to wrap the K/V ring."""
+    _run(kind, 2, 384, 384, 4, 2, 64, 64, seed=21)
+    _run(kind, 1, 1280, 1280, 2, 1, 64, 64, seed=22)
+    assert _kernel_status() == 0
+
+
+@pytest.mark.parametrize("d,dv", [(32, 32), (64, 32), (96, 96), (64, 128), (128, 64), (8, 8)])
+def test_padded_head_dims(d, dv, fwd_variant):
+    """Head dims below a variant's width: the columns past the end of a head must read as zeros and stay unwritten."""
+    _run("causal_doc", 1, 333, 333, 2, 1, d, dv, sink=True, seed=23)
+    _run("bidir_doc", 2, 256, 256, 2, 2, d, dv, seed=24)
+    assert _kernel_status() == 0
+
+
 @pytest.mark.parametrize("kind", ["none_causal", "causal_doc", "random_eviction"])
 def test_sink(kind, fwd_variant):
     _run(kind, 2, 256, 256, 4, 2, 128, 128, sink=True, seed=7)

@@ -152,8 +152,10 @@ def test_launch_order_bit_exact(Sq, Sk, mask_b, hm, monkeypatch):
     for w in range(3):
         assert torch.equal(single[w], fused[w]), w
     # no order where the kernel variant takes none, or without a mask tensor
-    a.d = a.dv = 64
+    a.d = a.dv = 256
     assert lib.fm_launch_order_ints(C.byref(a), _lib.FM_ORDER_FWD) == 0
+    a.d = a.dv = 64          # the 64-column tcgen05 variants read the same tables
+    assert lib.fm_launch_order_ints(C.byref(a), _lib.FM_ORDER_FWD) == sizes[0]
     a.d = a.dv = 128
     a.ncols = 0
     assert lib.fm_launch_order_ints(C.byref(a), _lib.FM_ORDER_BWD_DKDV) == 0
