@@ -54,6 +54,7 @@ SIGNATURES = {
     "fm_fwd_tile_shape": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "fm_bwd_tile_shape": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "fm_fwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
+    "fm_fwd_block_score": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "fm_launch_order_ints": (C.c_int64, [C.POINTER(AttnArgs), C.c_int]),
     "fm_launch_order": (C.c_int, [C.POINTER(AttnArgs), C.c_int, C.c_void_p, C.c_void_p]),
     "fm_launch_orders": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),

@@ -169,7 +169,10 @@ extern "C" int fm_bwd_tile_shape(int d, int dv, int* tile_m, int* tile_n) {
   return rc;
 }
 
-extern "C" int fm_fwd(const fm_attn_args* a, void* stream) {
+// Side output of the forward (fm_fwd_block_score); block_logit == nullptr: none.
+struct BlockScore { float* block_logit; const int32_t* block_bos; int block_size, block_ld; };
+
+static int fwd_impl(const fm_attn_args* a, const BlockScore& bs, void* stream) {
   int rc = validate_common(a, "fm_fwd");
   if (rc != FM_OK) return rc;
   int tm, tn;
@@ -180,6 +183,20 @@ extern "C" int fm_fwd(const fm_attn_args* a, void* stream) {
   AttnKParams p;
   fill_kparams(a, &p, false);
   p.md.nblk_pad = fm_mask_nblk_pad(a->Sk, tn);
+  if (bs.block_logit) {
+    FM_REQUIRE(fwd_uses_sm100(a->d, a->dv) && fwd_sm100_supported(a), FM_ERR_UNSUPPORTED,
+               "fm_fwd_block_score: only the tcgen05 forward (head dims <= 128, 16-byte aligned q/k/v) "
+               "writes block scores (d=%d, dv=%d)", a->d, a->dv);
+    FM_REQUIRE(bs.block_size == 32 || bs.block_size == 64 || bs.block_size == 128, FM_ERR_UNSUPPORTED,
+               "fm_fwd_block_score: block_size must be 32, 64 or 128 (got %d)", bs.block_size);
+    p.block_cols = (a->Sk + bs.block_size - 1) / bs.block_size;
+    FM_REQUIRE(bs.block_ld >= p.block_cols, FM_ERR_INVALID_ARGUMENT,
+               "fm_fwd_block_score: block_logit has %d blocks per row, ceil(Sk / block_size) = %d are needed",
+               bs.block_ld, p.block_cols);
+    p.block_logit = bs.block_logit; p.block_bos = bs.block_bos; p.block_ld = bs.block_ld;
+    p.block_log2 = bs.block_size == 32 ? 5 : (bs.block_size == 64 ? 6 : 7);
+    return fwd_sm100_launch(p, a, (cudaStream_t)stream);
+  }
   if (fwd_uses_sm100(a->d, a->dv) && fwd_sm100_supported(a)) {
     // with a launch table (a mask tensor) the persistent variant can walk it (FLASHMASK_B200_FWD_PERSIST=1);
     // the one-unit-per-CTA kernel reads its table entry at CTA start
@@ -192,6 +209,14 @@ extern "C" int fm_fwd(const fm_attn_args* a, void* stream) {
   FM_REQUIRE(!fwd_uses_sm100(a->d, a->dv), FM_ERR_INVALID_ARGUMENT,
              "fm_fwd: q/k/v must be 16-byte aligned");
   return fwd_mma_launch(p, a->dtype, (cudaStream_t)stream);
+}
+
+extern "C" int fm_fwd(const fm_attn_args* a, void* stream) { return fwd_impl(a, BlockScore{}, stream); }
+
+extern "C" int fm_fwd_block_score(const fm_attn_args* a, float* block_logit, int block_size, int block_ld,
+                                  const int32_t* block_bos, void* stream) {
+  FM_REQUIRE(block_logit != nullptr, FM_ERR_INVALID_ARGUMENT, "fm_fwd_block_score: block_logit is NULL");
+  return fwd_impl(a, BlockScore{block_logit, block_bos, block_size, block_ld}, stream);
 }
 
 // Geometry of a launch order: the ordered axis, rows per unit, the block the work is

@@ -23,6 +23,11 @@ struct AttnKParams {
   // variant runs on this table, 0 when the one-unit-per-CTA variant does (written by the table builder)
   int* dq_sched; int* dkdv_sched; int* fwd_sched;
   int dq_ncta, dkdv_ncta, fwd_ncta;   // entries of the tables
+  // optional side output of the forward: per (query row, block of key columns) the maximum of the
+  // masked, scaled scores, combined into block_logit[b][head][row][block] with fmax; block ids are
+  // relative to block_bos[b][row] (the first key of the row's document) when that is given
+  float* block_logit; const int32_t* block_bos;
+  int block_log2, block_cols, block_ld;   // log2(block size), ceil(Sk / block size), row stride
 };
 
 // CTA coordinates under a launch order: the CTAs of a launch are numbered in

@@ -68,7 +68,7 @@ struct FwdSm100Cfg {
 
 __device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
 
-template <int D, bool IS_BF16>
+template <int D, bool IS_BF16, bool BLOCK_SCORE>
 __global__ void __launch_bounds__(384, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const AttnKParams p) {
@@ -466,7 +466,7 @@ bool fwd_sm100_supported(const fm_attn_args* a) {
   return true;
 }
 
-template <int D, bool IS_BF16>
+template <int D, bool IS_BF16, bool BLOCK_SCORE>
 static int launch_fwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
   using Cfg = FwdSm100Cfg<D>;
   FM_REQUIRE((a->Sk + 127) / 128 <= Cfg::LIST_MAX, FM_ERR_UNSUPPORTED,
@@ -476,7 +476,7 @@ static int launch_fwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStr
   if ((rc = make_bshd_tmap(&tq, a->q, a->dtype, a->B, a->Sq, a->Hq, a->d, a->q_stride[0], a->q_stride[1], a->q_stride[2], 128))) return rc;
   if ((rc = make_bshd_tmap(&tk, a->k, a->dtype, a->B, a->Sk, a->Hkv, a->d, a->k_stride[0], a->k_stride[1], a->k_stride[2], 128))) return rc;
   if ((rc = make_bshd_tmap(&tv, a->v, a->dtype, a->B, a->Sk, a->Hkv, a->dv, a->v_stride[0], a->v_stride[1], a->v_stride[2], 128))) return rc;
-  auto kern = fwd_sm100_kernel<D, IS_BF16>;
+  auto kern = fwd_sm100_kernel<D, IS_BF16, BLOCK_SCORE>;
   FM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
   dim3 grid((p.Sq + 255) / 256, p.Hq, p.B);
   kern<<<grid, Cfg::NTHREADS, Cfg::SMEM, s>>>(tq, tk, tv, p);
@@ -486,8 +486,13 @@ static int launch_fwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStr
 
 int fwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
   const bool bf = a->dtype == FM_DTYPE_BF16;
-  if (a->d <= 64 && a->dv <= 64) return bf ? launch_fwd_sm100<64, true>(p, a, s) : launch_fwd_sm100<64, false>(p, a, s);
-  return bf ? launch_fwd_sm100<128, true>(p, a, s) : launch_fwd_sm100<128, false>(p, a, s);
+  const bool small = a->d <= 64 && a->dv <= 64;
+  if (p.block_logit) {
+    if (small) return bf ? launch_fwd_sm100<64, true, true>(p, a, s) : launch_fwd_sm100<64, false, true>(p, a, s);
+    return bf ? launch_fwd_sm100<128, true, true>(p, a, s) : launch_fwd_sm100<128, false, true>(p, a, s);
+  }
+  if (small) return bf ? launch_fwd_sm100<64, true, false>(p, a, s) : launch_fwd_sm100<64, false, false>(p, a, s);
+  return bf ? launch_fwd_sm100<128, true, false>(p, a, s) : launch_fwd_sm100<128, false, false>(p, a, s);
 }
 
 int fwd_sm100_status(int* out, bool reset) {

@@ -315,6 +315,39 @@ __device__ __forceinline__ uint64_t make_sdesc(uint32_t smem_addr, uint32_t lbo_
          ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
 }
 
+// Block maxima of one row of a 128-column tile (reference: the fused block-score epilogue,
+// flashmask/cute/flash_fwd_sm100.py:4256-4371).  `sr` holds the masked raw scores (masked =
+// -inf), `rel0` is the first column of the tile relative to the start of the row's document.
+// Column j falls into block (rel0 + j) >> log2(BS); a tile touches 128/BS blocks, one more
+// when rel0 is not a multiple of BS.  Each block maximum, scaled, is merged into the output
+// with fmax: a block can straddle two tiles, and the same thread owns the row in both.
+template <int BS>
+__device__ __forceinline__ void block_scores(const uint32_t* sr, int rel0, float scale, float* dst, int n_cols) {
+  constexpr int NS = 128 / BS;
+  constexpr int LOG2 = BS == 32 ? 5 : (BS == 64 ? 6 : 7);
+  float mx[NS + 1];
+#pragma unroll
+  for (int i = 0; i <= NS; ++i) mx[i] = __int_as_float(0xff800000);
+  const int t = BS - (rel0 & (BS - 1));     // columns of a block at or past t belong to the next block
+  if (t == BS) {
+#pragma unroll
+    for (int j = 0; j < 128; ++j) mx[j / BS] = fmaxf(mx[j / BS], __uint_as_float(sr[j]));
+  } else {
+#pragma unroll
+    for (int j = 0; j < 128; ++j) {
+      const float v = __uint_as_float(sr[j]);
+      if ((j % BS) >= t) mx[j / BS + 1] = fmaxf(mx[j / BS + 1], v);
+      else mx[j / BS] = fmaxf(mx[j / BS], v);
+    }
+  }
+  const int base = rel0 >> LOG2;            // arithmetic shift: floor for columns before the document
+#pragma unroll
+  for (int i = 0; i <= NS; ++i) {
+    const int rb = base + i;
+    if (rb >= 0 && rb < n_cols && (i < NS || t != BS)) dst[rb] = fmaxf(dst[rb], mx[i] * scale);
+  }
+}
+
 // host: driver entry point for tensor-map encoding, resolved once
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,

@@ -185,12 +185,21 @@ def _sink_fp32(sink, Hq, device):
 
 
 def _flash_attn_fwd(q, k, v, startend_row_indices=None, softmax_scale=None, causal=False,
-                    learnable_sink=None, return_lse=True, mask_info: Optional[FlashMaskInfo] = None):
+                    learnable_sink=None, return_lse=True, mask_info: Optional[FlashMaskInfo] = None,
+                    block_logit: Optional[torch.Tensor] = None, block_size: int = 64,
+                    block_bos: Optional[torch.Tensor] = None, pack_gqa: Optional[bool] = False):
     """Forward.  Returns (out [B,Sq,Hq,dv], lse [B,Hq,Sq] fp32).
 
+    With ``block_logit`` (fp32 ``[B, Hq, Sq, >= ceil(Sk / block_size)]``, filled with -inf by the
+    caller) the kernel also merges into it, with fmax, the maximum of the masked, scaled scores of
+    every (query row, block of ``block_size`` key columns); ``block_bos`` (int32 ``[B, Sq]``, first
+    key of the row's document) makes the block ids document-relative.  Queries are never packed
+    over the heads of a GQA group here, so ``pack_gqa`` must be False (or left at its default);
+    the reference defaults it to True under GQA and rejects that combination.
+
     Reference: _flash_attn_fwd, flashmask/cute/ops/fwd.py:52-882 (same argument
-    meaning; split-KV, pack-GQA and block-score outputs are not part of this
-    operator surface)."""
+    meaning; block-score arguments :75-77,605-658; split-KV and pack-GQA are not part of
+    this operator surface)."""
     if not q.is_cuda:
         raise RuntimeError("flashmask_b200 runs on CUDA (sm_100a) tensors only; there is no CPU path")
     idx = startend_row_indices
@@ -210,7 +219,30 @@ def _flash_attn_fwd(q, k, v, startend_row_indices=None, softmax_scale=None, caus
     a = _base_args(q, k, v, out, lse, idx, info, causal, softmax_scale, sink32)
     if info is not None:
         a.fwd_order = _launch_order(a, info, _lib.FM_ORDER_FWD, q)
-    _lib.check(_lib.load().fm_fwd(C.byref(a), _stream(q)), "fm_fwd")
+    if block_logit is None:
+        assert block_bos is None, "block_bos requires block_logit (it drives its relative bucketing)"
+        _lib.check(_lib.load().fm_fwd(C.byref(a), _stream(q)), "fm_fwd")
+        return out, lse
+    assert not pack_gqa, "block_logit requires pack_gqa=False: it is indexed by the query head and the query row"
+    assert block_logit.dtype == torch.float32, f"block_logit must be float32; got {block_logit.dtype}"
+    assert block_logit.is_cuda, "block_logit must be on CUDA"
+    assert block_logit.ndim == 4, (
+        f"block_logit must be [batch, num_heads, seqlen_q, num_blocks]; got ndim={block_logit.ndim}")
+    nb_min = -(-Sk // block_size)
+    assert tuple(block_logit.shape[:3]) == (B, Hq, Sq) and block_logit.is_contiguous(), (
+        f"block_logit must be a contiguous [B={B}, H={Hq}, S={Sq}, num_blocks]; got {tuple(block_logit.shape)}")
+    assert block_logit.shape[-1] >= nb_min, (
+        f"block_logit num_blocks={block_logit.shape[-1]} < ceil(seqlen_k/block_size)={nb_min}")
+    bos_ptr = None
+    if block_bos is not None:
+        assert block_bos.dtype == torch.int32, f"block_bos must be int32; got {block_bos.dtype}"
+        assert block_bos.is_cuda, "block_bos must be on CUDA"
+        assert tuple(block_bos.shape) == (B, Sq), f"block_bos must be [B={B}, S={Sq}]; got {tuple(block_bos.shape)}"
+        block_bos = block_bos.contiguous()
+        bos_ptr = block_bos.data_ptr()
+    _lib.check(_lib.load().fm_fwd_block_score(C.byref(a), block_logit.data_ptr(), int(block_size),
+                                              int(block_logit.shape[-1]), bos_ptr, _stream(q)),
+               "fm_fwd_block_score")
     return out, lse
 
 

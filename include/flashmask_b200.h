@@ -155,6 +155,24 @@ FM_API int fm_bwd_tile_shape(int d, int dv, int* tile_m, int* tile_n);
  * Uses no workspace. */
 FM_API int fm_fwd(const fm_attn_args* args, void* stream);
 
+/* fm_fwd with the fused block-score side output: besides O and LSE, for every
+ * query row and every block of `block_size` key columns the maximum of the
+ * masked, scaled scores softmax_scale * q.k (the values softmax is fed) is
+ * merged into
+ *   block_logit[((b * Hq + head) * Sq + row) * block_ld + block]   (fp32)
+ * with fmax.  Masked columns count as -inf.  Only the K tiles the attention
+ * loop visits are written, so the caller fills block_logit with -inf first.
+ * With block_bos ([B, Sq] int32, first key column of the row's document) block
+ * ids are relative to that column: block j of a row covers the columns
+ * [bos + j * block_size, bos + (j + 1) * block_size); NULL means bos = 0.
+ * block_size is 32, 64 or 128; block_ld >= ceil(Sk / block_size); O and LSE
+ * are bitwise those of fm_fwd.  FM_ERR_UNSUPPORTED for head dims above 128.
+ * Replaces the block_logit / block_size / block_bos arguments of
+ * _flash_attn_fwd (flashmask/cute/ops/fwd.py:75-77,605-658) and the fused
+ * epilogue of flashmask/cute/flash_fwd_sm100.py:4256-4371. */
+FM_API int fm_fwd_block_score(const fm_attn_args* args, float* block_logit, int block_size, int block_ld,
+                              const int32_t* block_bos, void* stream);
+
 /*
  * Longest-work-first launch order for sparse masks.  A kernel's CTAs are handed
  * to the SMs in launch order, so starting the heaviest tiles first keeps the

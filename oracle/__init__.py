@@ -15,6 +15,7 @@ classification bit patterns and the heap partition are not covered by any
 stored vector of the reference ("parity unpinned" for those three: the
 restatements here are the pins).
 """
-from .attention import dense_bias, attention_forward, attention_forward_backward  # noqa: F401
+from .attention import (dense_bias, attention_forward, attention_forward_backward,  # noqa: F401
+                        block_logit_ref)
 from .tiles import (nblk_pad, scan_max_min, valid_block_count, classify_tiles,  # noqa: F401
                     TILE_SKIP, TILE_PARTIAL, TILE_FULL)

@@ -130,3 +130,44 @@ def attention_forward_backward(q, k, v, d_out, idx=None, causal=False, sink=None
         p_sink = torch.where(torch.isinf(lse), torch.zeros_like(p_sink), p_sink)
         res["dsink"] = -(p_sink * dpsum).sum(dim=(0, 2))
     return res
+
+
+def block_logit_ref(q, k, idx=None, causal=False, softmax_scale=None, block_size=64,
+                    num_blocks=None, block_bos=None):
+    """Per (query row, block of key columns) maximum of the masked, scaled scores:
+    [B, Hq, Sq, num_blocks] fp32, -inf where every column of the block is masked (or outside the
+    sequence).
+
+    Restates the checker of the reference's fused block-score epilogue
+    (tests/paddle/test_block_score_fusion.py:62-87 ``ref_block_logit`` and :253-273 for GQA: scaled
+    logit ``softmax_scale * q.k``, masked columns -inf, columns padded to whole blocks with -inf,
+    max over each block) and extends it the way the kernel defines it
+    (flashmask/cute/flash_fwd_sm100.py:4273-4371): the mask is the attention's own (column bounds
+    and causal), and with ``block_bos`` ([B, Sq] int, first key column of the row's document) the
+    block of column j for row i is ``floor((j - bos[i]) / block_size)``; blocks below 0 or at or
+    past ``ceil(Sk / block_size)`` are dropped.  The reference's own test needs Paddle on an SM 10.x
+    GPU and cannot run where this file is checked: parity unpinned beyond this restatement."""
+    q = q.to(torch.float32); k = k.to(torch.float32)
+    B, Sq, Hq, d = q.shape
+    Sk = k.shape[1]
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
+    qh = q.permute(0, 2, 1, 3)
+    kh = _expand_heads(k.permute(0, 2, 1, 3), Hq)
+    scores = torch.matmul(qh, kh.transpose(-1, -2)) * scale
+    bias = dense_bias(None if idx is None else np.asarray(idx), Sq, Sk, causal)
+    if bias is not None:
+        bt = torch.from_numpy(bias)
+        if bt.shape[0] != B:
+            bt = bt.expand(B, -1, -1, -1)
+        scores = scores + _expand_heads(bt, Hq)
+    n_cols = -(-Sk // block_size)
+    nb = n_cols if num_blocks is None else num_blocks
+    out = torch.full((B, Hq, Sq, nb), float("-inf"), dtype=torch.float32)
+    bos = torch.zeros((B, Sq), dtype=torch.int64) if block_bos is None else torch.as_tensor(block_bos).to(torch.int64)
+    j = torch.arange(Sk, dtype=torch.int64)
+    blk = torch.div(j[None, None, :] - bos[:, :, None], block_size, rounding_mode="floor")   # [B, Sq, Sk]
+    ok = (blk >= 0) & (blk < n_cols)
+    blk = blk.clamp(0, nb - 1)[:, None].expand(B, Hq, Sq, Sk)
+    src = torch.where(ok[:, None].expand(B, Hq, Sq, Sk), scores, torch.full_like(scores, float("-inf")))
+    out.scatter_reduce_(3, blk, src, reduce="amax", include_self=True)
+    return out

@@ -68,3 +68,32 @@ def test_lse_definition():
         ref = torch.logsumexp(s[i, vis], 0) if vis else torch.tensor(-float("inf"))
         assert torch.allclose(lse[0, 0, i], ref, atol=1e-6)
     np.testing.assert_allclose(P.sum(-1)[0, 0].numpy(), 1.0, atol=1e-6)
+
+
+def test_block_logit_restatement_matches_the_reference_checker_formula():
+    """block_logit_ref against the literal formula of the reference's checker
+    (tests/paddle/test_block_score_fusion.py:62-87: scaled logits, causal -inf, pad to whole
+    blocks, reshape, max), and the document-relative ids against a per-row loop."""
+    import torch
+    g = torch.Generator().manual_seed(0)
+    B, S, Sk, Hq, Hkv, d, bs = 2, 70, 90, 4, 2, 16, 32
+    q = torch.randn(B, S, Hq, d, generator=g)
+    k = torch.randn(B, Sk, Hkv, d, generator=g)
+    scale = 1.0 / d ** 0.5
+    s = torch.einsum("bihd,bjhd->bhij", q, k.repeat_interleave(Hq // Hkv, dim=2)) * scale
+    i = torch.arange(S)[:, None]
+    j = torch.arange(Sk)[None, :]
+    s = s.masked_fill(j > i + (Sk - S), float("-inf"))
+    nb = -(-Sk // bs)
+    pad = torch.full((B, Hq, S, nb * bs - Sk), float("-inf"))
+    want = torch.cat([s, pad], -1).reshape(B, Hq, S, nb, bs).amax(-1)
+    got = oracle.block_logit_ref(q, k, None, True, None, bs)
+    assert torch.allclose(got, want, atol=1e-6) and torch.equal(torch.isinf(got), torch.isinf(want))
+    bos = torch.zeros(B, S, dtype=torch.int32)
+    bos[:, 33:] = 41
+    got = oracle.block_logit_ref(q, k, None, True, None, bs, block_bos=bos)
+    for b, h, r in ((0, 0, 5), (1, 3, 40), (0, 2, 69)):
+        for blk in range(nb):
+            lo, hi = int(bos[b, r]) + blk * bs, min(int(bos[b, r]) + (blk + 1) * bs, Sk)
+            w = s[b, h, r, lo:hi].max().item() if lo < hi else float("-inf")
+            assert got[b, h, r, blk].item() == pytest.approx(w, abs=1e-6) or (w == float("-inf") and got[b, h, r, blk].item() == w)
