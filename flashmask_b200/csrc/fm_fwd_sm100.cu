@@ -195,6 +195,15 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     float m_run = neg_inf(), l_run = 0.f;
     int n_done = 0, nbnd = 0;
     bool ok = true;
+    // block-score side output: this thread's row of it, and the first key of the row's document
+    float* bs_dst = nullptr;
+    int bs_bos = 0;
+    if constexpr (BLOCK_SCORE) {
+      if (row < p.Sq) {
+        bs_dst = p.block_logit + (((int64_t)b * p.Hq + hq) * p.Sq + row) * p.block_ld;
+        if (p.block_bos) bs_bos = p.block_bos[(int64_t)b * p.Sq + row];
+      }
+    }
     for (int i = 0; i < cnt && ok; ++i) {
       const uint32_t e = list[i];
       const uint32_t flags = (e >> (16 + 4 * s)) & 0xFu;
@@ -209,6 +218,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (!ok) break;
       }
       if (flags) {
+        int bs_rel0 = 0;
+        float bs_old[5];
+        if constexpr (BLOCK_SCORE) {
+          bs_rel0 = (int)(e & 0xFFFFu) * 128 - bs_bos;
+          if (row < p.Sq) block_scores_prefetch(bs_rel0, p.block_log2, bs_dst, p.block_cols, bs_old);
+        }
         ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_SFULL + s), (uint32_t)n_done & 1u, wc));
         if (!ok) break;
         if (tid == 0 && n_done == 0) FPROF(2);

@@ -123,6 +123,7 @@ fwd_sm100_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     uint8_t* stg = smem + Cfg::OFF_EPI + warp * Cfg::EPI_BYTES;   // 32 rows x 64 bytes, 16-byte pieces XOR-swizzled
     const float scale_log2 = p.scale_log2;
     constexpr bool BLOCK_SCORE = false;        // the block-score side output is served by the one-unit kernel
+    const int bs_rel0 = 0; float* const bs_dst = nullptr; const float* const bs_old = nullptr;
     int n_tot = 0, nbnd = 0;                   // tiles of this sub-tile / bounds slots over the life of the CTA
     bool ok = true;
     for (int j = 0; ok; ++j) {

@@ -321,8 +321,20 @@ __device__ __forceinline__ uint64_t make_sdesc(uint32_t smem_addr, uint32_t lbo_
 // Column j falls into block (rel0 + j) >> log2(BS); a tile touches 128/BS blocks, one more
 // when rel0 is not a multiple of BS.  Each block maximum, scaled, is merged into the output
 // with fmax: a block can straddle two tiles, and the same thread owns the row in both.
+// The values already there (`old`) are fetched by block_scores_prefetch before the thread
+// waits for the scores of the tile, so that the read-modify-write adds no load latency to
+// the softmax critical path.
+__device__ __forceinline__ void block_scores_prefetch(int rel0, int log2_bs, const float* dst, int n_cols, float* old) {
+  const int base = rel0 >> log2_bs, ns = 128 >> log2_bs;
+#pragma unroll
+  for (int i = 0; i < 5; ++i) {
+    const int rb = base + i;
+    old[i] = (i <= ns && rb >= 0 && rb < n_cols) ? dst[rb] : __int_as_float(0xff800000);
+  }
+}
 template <int BS>
-__device__ __forceinline__ void block_scores(const uint32_t* sr, int rel0, float scale, float* dst, int n_cols) {
+__device__ __forceinline__ void block_scores(const uint32_t* sr, int rel0, float scale, float* dst, int n_cols,
+                                             const float* old) {
   constexpr int NS = 128 / BS;
   constexpr int LOG2 = BS == 32 ? 5 : (BS == 64 ? 6 : 7);
   float mx[NS + 1];
@@ -344,7 +356,7 @@ __device__ __forceinline__ void block_scores(const uint32_t* sr, int rel0, float
 #pragma unroll
   for (int i = 0; i <= NS; ++i) {
     const int rb = base + i;
-    if (rb >= 0 && rb < n_cols && (i < NS || t != BS)) dst[rb] = fmaxf(dst[rb], mx[i] * scale);
+    if (rb >= 0 && rb < n_cols && (i < NS || t != BS)) dst[rb] = fmaxf(old[i], mx[i] * scale);
   }
 }
 

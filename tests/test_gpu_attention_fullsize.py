@@ -25,10 +25,11 @@ FULL = ["causal_doc_8k_gqa", "sweep32k_sliding_window", "sweep32k_causal_doc", "
         "sweep32k_bidir_doc", "sweep32k_random_eviction"]
 
 
-def _setup(name, seed=0):
+def _setup(name, seed=0, d=None):
     w = W.make_workload(name)
+    d = d or w.d
     g = torch.Generator().manual_seed(seed)
-    q, k, v, do = (torch.randn(w.B, s, h, w.d, generator=g).to(torch.bfloat16).cuda()
+    q, k, v, do = (torch.randn(w.B, s, h, d, generator=g).to(torch.bfloat16).cuda()
                    for s, h in ((w.Sq, w.Hq), (w.Sk, w.Hkv), (w.Sk, w.Hkv), (w.Sq, w.Hq)))
     idx = torch.from_numpy(np.ascontiguousarray(w.idx).copy()).cuda()
     return w, q, k, v, do, idx
@@ -40,9 +41,14 @@ def _fwd_bwd(w, q, k, v, do, idx):
     return out, lse, dq, dk, dv
 
 
-@pytest.mark.parametrize("name", FULL)
-def test_rows_sum_to_one_and_gradients_of_constant_values(name):
-    w, q, k, v, do, idx = _setup(name)
+# the same masks at the head dims of the 64-column variants and of the zero-filled 128-column one
+SMALL_D = [("causal_doc_8k_gqa", 64), ("causal_doc_8k_gqa", 96), ("sweep32k_share_question", 64),
+           ("sweep32k_bidir_doc", 64)]
+
+
+@pytest.mark.parametrize("name,d", [(n, None) for n in FULL] + SMALL_D)
+def test_rows_sum_to_one_and_gradients_of_constant_values(name, d):
+    w, q, k, v, do, idx = _setup(name, d=d)
     ones_v, ones_do = torch.ones_like(v), torch.ones_like(do)
     out, lse, dq, dk, dv = _fwd_bwd(w, q, k, ones_v, ones_do, idx)
     seen = torch.isfinite(lse)                                  # [B, Hq, Sq]
@@ -53,8 +59,8 @@ def test_rows_sum_to_one_and_gradients_of_constant_values(name):
     # the mask's own count of visible pairs says which (b, head) pairs can have empty rows at all
     n_vis = fm.count_visible(idx, w.Sq, w.causal)
     assert int(n_vis.min()) > 0
-    # score gradient ~ 0: dP - rowsum(dO*O) = 128 - 128*O is 0 wherever O rounded to exactly 1 and one bf16
-    # step (0.5 or 1) on the few rows where it did not
+    # score gradient ~ 0: dP - rowsum(dO*O) = dv - dv*O is 0 wherever O rounded to exactly 1 and one bf16
+    # step (0.5 or 1 at dv = 128) on the few rows where it did not
     assert dq.float().abs().max().item() < 1.0 and dk.float().abs().max().item() < 1.0
     assert dq.float().abs().mean().item() < 0.02 and dk.float().abs().mean().item() < 0.02
     # every column of dV adds up the rows of P of the q heads of its group: the rows that see a key
@@ -76,9 +82,11 @@ def test_forward_is_linear_in_values(name):
     assert err < 0.06, err          # three bf16 roundings of values of size ~1
 
 
-@pytest.mark.parametrize("name", ["causal_doc_8k_gqa", "sweep32k_causal_doc", "sweep32k_random_eviction"])
-def test_tcgen05_and_warp_mma_kernels_agree(name, monkeypatch):
-    w, q, k, v, do, idx = _setup(name, seed=2)
+@pytest.mark.parametrize("name,d", [("causal_doc_8k_gqa", None), ("sweep32k_causal_doc", None),
+                                    ("sweep32k_random_eviction", None), ("causal_doc_8k_gqa", 64),
+                                    ("causal_doc_8k_gqa", 80), ("sweep32k_random_eviction", 64)])
+def test_tcgen05_and_warp_mma_kernels_agree(name, d, monkeypatch):
+    w, q, k, v, do, idx = _setup(name, seed=2, d=d)
     a = _fwd_bwd(w, q, k, v, do, idx)
     monkeypatch.setenv("FLASHMASK_B200_FWD", "mma")
     monkeypatch.setenv("FLASHMASK_B200_BWD", "mma")
