@@ -56,6 +56,10 @@ struct FwdSm100Cfg {
   static constexpr int OFF_BAR = OFF_LIST + LIST_MAX * 4;
   static constexpr int OFF_MISC = OFF_BAR + 32 * 8;
   static constexpr int SMEM = OFF_MISC + 64 + 1024;     // + alignment slack
+  // block-score variant only: 16 block maxima per softmax thread behind everything else
+  static constexpr int OFF_BS = OFF_MISC + 64;
+  static constexpr int SMEM_BS = OFF_BS + 16 * BS_ACC_STRIDE * 4 + 1024;
+  static_assert(SMEM_BS <= 227 * 1024, "shared memory of the block-score variant");
   // barrier indices
   static constexpr int B_QFULL = 0, B_KVFULL = 2, B_KVEMPTY = 2 + NSTAGE, B_SFULL = 2 + 2 * NSTAGE,
                        B_PFULL = B_SFULL + 2, B_ODONE = B_PFULL + 2, B_BNDFULL = B_ODONE + 2,
@@ -68,7 +72,9 @@ struct FwdSm100Cfg {
 
 __device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
 
-template <int D, bool IS_BF16, bool BLOCK_SCORE>
+// BLOCK_SCORE: 0, or the block size (32 / 64 / 128) of the block-score side output; BLOCK_BOS: document
+// starts are given, so a block may straddle two tiles.
+template <int D, bool IS_BF16, int BLOCK_SCORE, bool BLOCK_BOS>
 __global__ void __launch_bounds__(384, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const AttnKParams p) {
@@ -196,14 +202,48 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     int n_done = 0, nbnd = 0;
     bool ok = true;
     // block-score side output: this thread's row of it, and the first key of the row's document
+    // Block scores.  A row whose document starts on a block boundary (always, without block_bos) has
+    // every block inside one tile: the maxima are stored straight from registers.  Otherwise a block
+    // can straddle two tiles, and the maxima are gathered per thread in shared memory, sixteen
+    // consecutive blocks of the row (two groups of eight); a group is merged into global memory once
+    // no later tile can touch it: tiles are walked right to left, so its turn comes when a tile lies
+    // wholly below it.  The merge (load, fmax, store of 32 contiguous bytes per row) runs BEFORE the
+    // thread waits for the scores of the next tile, where its load latency overlaps the tensor pipe.
     float* bs_dst = nullptr;
-    int bs_bos = 0;
-    if constexpr (BLOCK_SCORE) {
-      if (row < p.Sq) {
-        bs_dst = p.block_logit + (((int64_t)b * p.Hq + hq) * p.Sq + row) * p.block_ld;
-        if (p.block_bos) bs_bos = p.block_bos[(int64_t)b * p.Sq + row];
+    float* bs_acc = nullptr;
+    int bs_bos = 0, bs_pend_lo = INT_MAX, bs_pend_hi = -1;    // pending groups [lo, hi]; lo > hi: none
+    bool bs_vec = false;
+    if constexpr (BLOCK_SCORE != 0) {
+      if (row < p.Sq) bs_dst = p.block_logit + (((int64_t)b * p.Hq + hq) * p.Sq + row) * p.block_ld;
+      if constexpr (BLOCK_BOS) {
+        bs_acc = reinterpret_cast<float*>(smem + Cfg::OFF_BS) + tid;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) bs_acc[c * BS_ACC_STRIDE] = neg_inf();
+        if (row < p.Sq) {
+          bs_bos = p.block_bos[(int64_t)b * p.Sq + row];
+          bs_vec = (reinterpret_cast<uintptr_t>(bs_dst) & 15) == 0;
+        }
       }
     }
+    auto bs_flush = [&](int g) {
+      float* gp = bs_dst + g * 8;
+      float* a = bs_acc + (g & 1) * 8 * BS_ACC_STRIDE;
+      if (bs_vec && g * 8 + 7 < p.block_cols) {
+        float4 o0 = *reinterpret_cast<const float4*>(gp), o1 = *reinterpret_cast<const float4*>(gp + 4);
+        o0.x = fmaxf(o0.x, a[0 * BS_ACC_STRIDE]); o0.y = fmaxf(o0.y, a[1 * BS_ACC_STRIDE]);
+        o0.z = fmaxf(o0.z, a[2 * BS_ACC_STRIDE]); o0.w = fmaxf(o0.w, a[3 * BS_ACC_STRIDE]);
+        o1.x = fmaxf(o1.x, a[4 * BS_ACC_STRIDE]); o1.y = fmaxf(o1.y, a[5 * BS_ACC_STRIDE]);
+        o1.z = fmaxf(o1.z, a[6 * BS_ACC_STRIDE]); o1.w = fmaxf(o1.w, a[7 * BS_ACC_STRIDE]);
+        *reinterpret_cast<float4*>(gp) = o0;
+        *reinterpret_cast<float4*>(gp + 4) = o1;
+      } else {
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          if (g * 8 + c < p.block_cols) gp[c] = fmaxf(gp[c], a[c * BS_ACC_STRIDE]);
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) a[c * BS_ACC_STRIDE] = neg_inf();
+    };
     for (int i = 0; i < cnt && ok; ++i) {
       const uint32_t e = list[i];
       const uint32_t flags = (e >> (16 + 4 * s)) & 0xFu;
@@ -219,10 +259,22 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
       if (flags) {
         int bs_rel0 = 0;
-        float bs_old[5];
-        if constexpr (BLOCK_SCORE) {
-          bs_rel0 = (int)(e & 0xFFFFu) * 128 - bs_bos;
-          if (row < p.Sq) block_scores_prefetch(bs_rel0, p.block_log2, bs_dst, p.block_cols, bs_old);
+        if constexpr (BLOCK_SCORE != 0) bs_rel0 = (int)(e & 0xFFFFu) * 128 - bs_bos;
+        if constexpr (BLOCK_SCORE != 0 && BLOCK_BOS) {
+          constexpr int BS_LOG2 = BLOCK_SCORE == 32 ? 5 : (BLOCK_SCORE == 64 ? 6 : 7);
+          if (bs_dst && (bs_rel0 & ((1 << BS_LOG2) - 1)) != 0) {
+            // blocks this tile can touch: [base, top]; the groups above them are complete
+            const int base = bs_rel0 >> BS_LOG2;
+            const int top = base + (128 >> BS_LOG2);
+            const int lo_rb = max(base, 0), hi_rb = min(top, p.block_cols - 1);
+            if (lo_rb <= hi_rb) {
+              const int g_top = hi_rb >> 3, g_bot = lo_rb >> 3;
+              for (int g = bs_pend_hi; g >= max(bs_pend_lo, g_top + 1); --g) bs_flush(g);
+              bs_pend_hi = min(bs_pend_hi, g_top);
+              if (bs_pend_lo > bs_pend_hi) { bs_pend_hi = g_top; bs_pend_lo = g_bot; }
+              else bs_pend_lo = min(bs_pend_lo, g_bot);
+            }
+          }
         }
         ok = __all_sync(0xffffffffu, mbar_wait(bar(Cfg::B_SFULL + s), (uint32_t)n_done & 1u, wc));
         if (!ok) break;
@@ -241,6 +293,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         mbar_arrive(bar(Cfg::B_BNDEMPTY + bslot));
         ++nbnd;
       }
+    }
+    if constexpr (BLOCK_SCORE != 0 && BLOCK_BOS) {
+      if (ok && bs_dst)
+        for (int g = bs_pend_hi; g >= bs_pend_lo; --g) bs_flush(g);
     }
     // ---- epilogue: O / l -> bf16 -> smem staging -> coalesced stores; LSE ----
     if (tid == 0) FPROF(3);
@@ -481,7 +537,7 @@ bool fwd_sm100_supported(const fm_attn_args* a) {
   return true;
 }
 
-template <int D, bool IS_BF16, bool BLOCK_SCORE>
+template <int D, bool IS_BF16, int BLOCK_SCORE, bool BLOCK_BOS>
 static int launch_fwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
   using Cfg = FwdSm100Cfg<D>;
   FM_REQUIRE((a->Sk + 127) / 128 <= Cfg::LIST_MAX, FM_ERR_UNSUPPORTED,
@@ -491,10 +547,11 @@ static int launch_fwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStr
   if ((rc = make_bshd_tmap(&tq, a->q, a->dtype, a->B, a->Sq, a->Hq, a->d, a->q_stride[0], a->q_stride[1], a->q_stride[2], 128))) return rc;
   if ((rc = make_bshd_tmap(&tk, a->k, a->dtype, a->B, a->Sk, a->Hkv, a->d, a->k_stride[0], a->k_stride[1], a->k_stride[2], 128))) return rc;
   if ((rc = make_bshd_tmap(&tv, a->v, a->dtype, a->B, a->Sk, a->Hkv, a->dv, a->v_stride[0], a->v_stride[1], a->v_stride[2], 128))) return rc;
-  auto kern = fwd_sm100_kernel<D, IS_BF16, BLOCK_SCORE>;
-  FM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+  auto kern = fwd_sm100_kernel<D, IS_BF16, BLOCK_SCORE, BLOCK_BOS>;
+  constexpr int smem_bytes = BLOCK_BOS ? Cfg::SMEM_BS : Cfg::SMEM;
+  FM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   dim3 grid((p.Sq + 255) / 256, p.Hq, p.B);
-  kern<<<grid, Cfg::NTHREADS, Cfg::SMEM, s>>>(tq, tk, tv, p);
+  kern<<<grid, Cfg::NTHREADS, smem_bytes, s>>>(tq, tk, tv, p);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }
@@ -502,12 +559,24 @@ static int launch_fwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStr
 int fwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
   const bool bf = a->dtype == FM_DTYPE_BF16;
   const bool small = a->d <= 64 && a->dv <= 64;
-  if (p.block_logit) {
-    if (small) return bf ? launch_fwd_sm100<64, true, true>(p, a, s) : launch_fwd_sm100<64, false, true>(p, a, s);
-    return bf ? launch_fwd_sm100<128, true, true>(p, a, s) : launch_fwd_sm100<128, false, true>(p, a, s);
+#define FM_FWD_DISPATCH(BSZ, BOS)                                                                         \
+  do {                                                                                                    \
+    if (small)                                                                                            \
+      return bf ? launch_fwd_sm100<64, true, BSZ, BOS>(p, a, s) : launch_fwd_sm100<64, false, BSZ, BOS>(p, a, s); \
+    return bf ? launch_fwd_sm100<128, true, BSZ, BOS>(p, a, s) : launch_fwd_sm100<128, false, BSZ, BOS>(p, a, s); \
+  } while (0)
+  if (p.block_logit && p.block_bos) {
+    if (p.block_log2 == 5) FM_FWD_DISPATCH(32, true);
+    if (p.block_log2 == 6) FM_FWD_DISPATCH(64, true);
+    FM_FWD_DISPATCH(128, true);
   }
-  if (small) return bf ? launch_fwd_sm100<64, true, false>(p, a, s) : launch_fwd_sm100<64, false, false>(p, a, s);
-  return bf ? launch_fwd_sm100<128, true, false>(p, a, s) : launch_fwd_sm100<128, false, false>(p, a, s);
+  if (p.block_logit) {
+    if (p.block_log2 == 5) FM_FWD_DISPATCH(32, false);
+    if (p.block_log2 == 6) FM_FWD_DISPATCH(64, false);
+    FM_FWD_DISPATCH(128, false);
+  }
+  FM_FWD_DISPATCH(0, false);
+#undef FM_FWD_DISPATCH
 }
 
 int fwd_sm100_status(int* out, bool reset) {

@@ -122,8 +122,8 @@ fwd_sm100_persist_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
     const uint32_t tO = tmem + lane_field + 256u + 128u * s;
     uint8_t* stg = smem + Cfg::OFF_EPI + warp * Cfg::EPI_BYTES;   // 32 rows x 64 bytes, 16-byte pieces XOR-swizzled
     const float scale_log2 = p.scale_log2;
-    constexpr bool BLOCK_SCORE = false;        // the block-score side output is served by the one-unit kernel
-    const int bs_rel0 = 0; float* const bs_dst = nullptr; const float* const bs_old = nullptr;
+    constexpr int BLOCK_SCORE = 0; constexpr bool BLOCK_BOS = false;       // the block-score side output is served by the one-unit kernel
+    const int bs_rel0 = 0; float* const bs_dst = nullptr; float* const bs_acc = nullptr;
     int n_tot = 0, nbnd = 0;                   // tiles of this sub-tile / bounds slots over the life of the CTA
     bool ok = true;
     for (int j = 0; ok; ++j) {

@@ -318,46 +318,71 @@ __device__ __forceinline__ uint64_t make_sdesc(uint32_t smem_addr, uint32_t lbo_
 // Block maxima of one row of a 128-column tile (reference: the fused block-score epilogue,
 // flashmask/cute/flash_fwd_sm100.py:4256-4371).  `sr` holds the masked raw scores (masked =
 // -inf), `rel0` is the first column of the tile relative to the start of the row's document.
-// Column j falls into block (rel0 + j) >> log2(BS); a tile touches 128/BS blocks, one more
-// when rel0 is not a multiple of BS.  Each block maximum, scaled, is merged into the output
-// with fmax: a block can straddle two tiles, and the same thread owns the row in both.
-// The values already there (`old`) are fetched by block_scores_prefetch before the thread
-// waits for the scores of the tile, so that the read-modify-write adds no load latency to
-// the softmax critical path.
-__device__ __forceinline__ void block_scores_prefetch(int rel0, int log2_bs, const float* dst, int n_cols, float* old) {
-  const int base = rel0 >> log2_bs, ns = 128 >> log2_bs;
-#pragma unroll
-  for (int i = 0; i < 5; ++i) {
-    const int rb = base + i;
-    old[i] = (i <= ns && rb >= 0 && rb < n_cols) ? dst[rb] : __int_as_float(0xff800000);
-  }
-}
-template <int BS>
-__device__ __forceinline__ void block_scores(const uint32_t* sr, int rel0, float scale, float* dst, int n_cols,
-                                             const float* old) {
+// Column j falls into block (rel0 + j) >> log2(BS).
+//   * rel0 a multiple of BS: the tile holds 128/BS whole blocks and nothing else contributes
+//     to them; their scaled maxima are stored to `dst` (the thread's row of the output; NULL
+//     for a row past the end of the sequence) as they are.
+//   * otherwise the tile touches 128/BS + 1 blocks and the outer two straddle its
+//     neighbours: the scaled maxima are merged (fmax) into this thread's accumulators in
+//     shared memory, `acc[(block & 15) * BS_ACC_STRIDE]`, sixteen consecutive blocks of the
+//     row in two groups of eight, which the caller merges into `dst` a group at a time.
+// Returns the maximum over the whole row of the tile (the row maximum of the online softmax
+// is the maximum of the block maxima, so it is not computed a second time).
+constexpr int BS_ACC_STRIDE = 256;
+// STRADDLE = false compiles the second case out (no document starts given: rel0 is a multiple of 128).
+template <int BS, bool STRADDLE>
+__device__ __forceinline__ float block_scores(const uint32_t* sr, int rel0, float scale, float* acc, int n_cols,
+                                              float* dst) {
   constexpr int NS = 128 / BS;
   constexpr int LOG2 = BS == 32 ? 5 : (BS == 64 ? 6 : 7);
-  float mx[NS + 1];
-#pragma unroll
-  for (int i = 0; i <= NS; ++i) mx[i] = __int_as_float(0xff800000);
-  const int t = BS - (rel0 & (BS - 1));     // columns of a block at or past t belong to the next block
-  if (t == BS) {
-#pragma unroll
-    for (int j = 0; j < 128; ++j) mx[j / BS] = fmaxf(mx[j / BS], __uint_as_float(sr[j]));
-  } else {
-#pragma unroll
-    for (int j = 0; j < 128; ++j) {
-      const float v = __uint_as_float(sr[j]);
-      if ((j % BS) >= t) mx[j / BS + 1] = fmaxf(mx[j / BS + 1], v);
-      else mx[j / BS] = fmaxf(mx[j / BS], v);
-    }
-  }
+  constexpr int NC = BS == 32 ? 2 : 4;      // independent fmax chains per block (instruction-level parallelism)
   const int base = rel0 >> LOG2;            // arithmetic shift: floor for columns before the document
+  const int t = BS - (rel0 & (BS - 1));     // columns of a block at or past t belong to the next block
+  if (!STRADDLE || t == BS) {
+    float part[NS][NC];
+#pragma unroll
+    for (int i = 0; i < NS; ++i)
+#pragma unroll
+      for (int c = 0; c < NC; ++c) part[i][c] = __int_as_float(0xff800000);
+#pragma unroll
+    for (int j = 0; j < 128; ++j) part[j / BS][j % NC] = fmaxf(part[j / BS][j % NC], __uint_as_float(sr[j]));
+    float all = __int_as_float(0xff800000);
+#pragma unroll
+    for (int i = 0; i < NS; ++i) {
+      float m = part[i][0];
+#pragma unroll
+      for (int c = 1; c < NC; ++c) m = fmaxf(m, part[i][c]);
+      all = fmaxf(all, m);
+      const int rb = base + i;
+      if (dst && rb >= 0 && rb < n_cols) dst[rb] = m * scale;
+    }
+    return all;
+  }
+  float part[NS + 1][NC];
+#pragma unroll
+  for (int i = 0; i <= NS; ++i)
+#pragma unroll
+    for (int c = 0; c < NC; ++c) part[i][c] = __int_as_float(0xff800000);
+#pragma unroll
+  for (int j = 0; j < 128; ++j) {
+    const float v = __uint_as_float(sr[j]);
+    if ((j % BS) >= t) part[j / BS + 1][j % NC] = fmaxf(part[j / BS + 1][j % NC], v);
+    else part[j / BS][j % NC] = fmaxf(part[j / BS][j % NC], v);
+  }
+  float all = __int_as_float(0xff800000);
 #pragma unroll
   for (int i = 0; i <= NS; ++i) {
+    float m = part[i][0];
+#pragma unroll
+    for (int c = 1; c < NC; ++c) m = fmaxf(m, part[i][c]);
+    all = fmaxf(all, m);
     const int rb = base + i;
-    if (rb >= 0 && rb < n_cols && (i < NS || t != BS)) dst[rb] = fmaxf(old[i], mx[i] * scale);
+    if (dst && rb >= 0 && rb < n_cols) {
+      float* a = acc + (rb & 15) * BS_ACC_STRIDE;
+      *a = fmaxf(*a, m * scale);
+    }
   }
+  return all;
 }
 
 // host: driver entry point for tensor-map encoding, resolved once

@@ -157,11 +157,12 @@ FM_API int fm_fwd(const fm_attn_args* args, void* stream);
 
 /* fm_fwd with the fused block-score side output: besides O and LSE, for every
  * query row and every block of `block_size` key columns the maximum of the
- * masked, scaled scores softmax_scale * q.k (the values softmax is fed) is
- * merged into
- *   block_logit[((b * Hq + head) * Sq + row) * block_ld + block]   (fp32)
- * with fmax.  Masked columns count as -inf.  Only the K tiles the attention
- * loop visits are written, so the caller fills block_logit with -inf first.
+ * masked, scaled scores softmax_scale * q.k (the values softmax is fed) goes to
+ *   block_logit[((b * Hq + head) * Sq + row) * block_ld + block]   (fp32).
+ * Masked columns count as -inf.  Only the K tiles the attention loop visits are
+ * written, so the caller fills block_logit with -inf first; a block that lies
+ * inside one K tile is stored as it is, a block that straddles two tiles (only
+ * possible with block_bos) is merged into the entry with fmax.
  * With block_bos ([B, Sq] int32, first key column of the row's document) block
  * ids are relative to that column: block j of a row covers the columns
  * [bos + j * block_size, bos + (j + 1) * block_size); NULL means bos = 0.
