@@ -386,8 +386,10 @@ def main():
     roofline = {"bound": "tensor", "kernel": "fm_bwd (preprocess + dK/dV + dQ kernels)" if dom == "bwd" else "fm_fwd kernel",
                 "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / peak_tf,
                 "peak_source": peak_src,
-                "traffic": NCU_DRAM_BYTES[dom], "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, "
-                "one capture of this workload (profiles/fwd_bwd_sm100_kernels_causal_doc_8k_gqa_ncu_full.md)",
+                "traffic": NCU_DRAM_BYTES[dom] if name == "causal_doc_8k_gqa" else None,
+                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, "
+                "one capture of this workload (profiles/fwd_bwd_sm100_kernels_causal_doc_8k_gqa_ncu_full.md)"
+                if name == "causal_doc_8k_gqa" else "no capture of this workload",
                 "fwd_ms": ms_fwd, "bwd_ms": ms_bwd, "mask_prep_ms": ms_prep,
                 "fwd_tflops": fwd_flops / (ms_fwd * 1e-3) / 1e12,
                 "bwd_tflops": bwd_flops / (ms_bwd * 1e-3) / 1e12}

@@ -319,12 +319,13 @@ def make_workload(name: str, S: Optional[int] = None) -> Workload:
         rng = np.random.default_rng(0)
         idx, causal = causal_document(1, S, S, uniform_doc_lengths(rng, S, 4))
         return Workload(name, 1, S, S, 2, 2, 64, 64, idx, causal, seed=0)
-    if name == "causal_doc_8k_gqa":            # the headline single-GPU case
+    if name in ("causal_doc_8k_gqa", "causal_doc_8k_gqa_d64"):   # the headline single-GPU case; the same mask at d = 64
         S = S or 8192
         rng = np.random.default_rng(1)
         docs = _docs_per_batch(rng, 2, S, math.log(1024), 1.0, 64, 8192)
         idx = _cat_batches([causal_document(1, S, S, d)[0] for d in docs])
-        return Workload(name, 2, S, S, 32, 8, 128, 128, idx, True, seed=1)
+        hd = 64 if name.endswith("_d64") else 128
+        return Workload(name, 2, S, S, 32, 8, hd, hd, idx, True, seed=1)
     if name.startswith("sweep32k_"):
         S = S or 32768
         kind = name[len("sweep32k_"):]
@@ -366,7 +367,7 @@ def make_workload(name: str, S: Optional[int] = None) -> Workload:
 
 
 WORKLOADS = [
-    "cpu_causal_doc_1k", "causal_doc_8k_gqa",
+    "cpu_causal_doc_1k", "causal_doc_8k_gqa", "causal_doc_8k_gqa_d64",
     "sweep32k_sliding_window", "sweep32k_causal_doc", "sweep32k_share_question",
     "sweep32k_bidir_doc", "sweep32k_random_eviction",
     "bigd16k_192_128", "bigd16k_576_512", "bigd16k_256_256",
