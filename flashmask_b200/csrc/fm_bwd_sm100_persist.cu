@@ -94,20 +94,12 @@ __device__ __forceinline__ void pbulk_copy_g2s(uint32_t dst, const void* src, ui
                : "memory");
 }
 
-// L2 prefetch of one TMA box (no shared-memory destination, no barrier)
-__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* tmap, int c0, int c1, int c2, int c3) {
-  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
-               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-               : "memory");
-}
-
 // A CTA works through a sequence of UNITS (one stationary 128-row tile each: a K/V tile in
 // MODE_DKDV, a Q/dO tile in MODE_DQ).  Without a launch table it owns exactly the unit its
 // block index names.  With one (p.*_order + p.*_sched) the launch is persistent: units are
 // fetched from the table through a global counter, and while one unit is in its main loop
-// the scheduler warp already fetches the next one, builds its work list and prefetches its
-// stationary tile into L2, so that entry, list build and most of the first loads disappear
-// from the critical path of short units.
+// the scheduler warp already fetches the next one and builds its work list, so that entry and
+// list build disappear from the critical path of short units.
 // D: width the head dims are computed at (64 when both fit, else 128); the 64-column variant keeps
 // the shared-memory layout and leaves the second 64-column sub-tile of every operand unloaded.
 template <int MODE, bool IS_BF16, int D>

@@ -153,6 +153,7 @@ def test_mask_heads_per_kv_head(fwd_variant):
 
 def test_fp16(fwd_variant):
     _run("causal_doc", 1, 256, 256, 2, 2, 128, 128, seed=9, dtype=torch.float16)
+    _run("bidir_doc", 1, 384, 384, 4, 2, 64, 64, seed=10, dtype=torch.float16)
 
 
 def test_long_rows_many_tiles(fwd_variant):
@@ -325,3 +326,40 @@ def test_shared_kv_convention():
     want[..., :dv] += dv2.float()
     assert torch.equal(dq, dq2)
     assert (dk.float() - want).abs().max().item() <= 2 ** -6 * max(1.0, want.abs().max().item())
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_forward_and_backward_replay_from_a_cuda_graph(d):
+    """fm_fwd / fm_bwd synchronise nothing and allocate nothing: with the mask prepared and the launch
+    tables built beforehand, forward + backward capture into one CUDA graph, and a replay on new input
+    values gives the bits of an eager run (the persistent kernels rewind their own table counters)."""
+    B, S, Hq, Hkv = 2, 1024, 4, 2
+    idx_np, causal = _mask("causal_doc", B, S, S, 41)
+    idx = torch.from_numpy(np.ascontiguousarray(idx_np).copy()).cuda()
+    a = [t.cuda() for t in make_inputs(B, S, S, Hq, Hkv, d, d, 42)[:4]]
+    b = [t.cuda() for t in make_inputs(B, S, S, Hq, Hkv, d, d, 43)[:4]]
+    info = fm.prepare_mask(idx, S, causal, *fm.fwd_tile_shape(d, d))
+
+    def step(q, k, v, do):
+        out, lse = fm._flash_attn_fwd(q, k, v, idx, causal=causal, mask_info=info)
+        dq, dk, dv, _ = fm._flash_attn_bwd(q, k, v, out, do, lse, idx, causal=causal, mask_info=info)
+        return out, lse, dq, dk, dv
+
+    want = [t.clone() for t in step(*b)]            # eager; also builds the launch tables
+    static = [t.clone() for t in a]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step(*static)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        got = step(*static)
+    for s_, n_ in zip(static, b):
+        s_.copy_(n_)
+    graph.replay()
+    graph.replay()                                   # a second replay: the table counters were rewound
+    torch.cuda.synchronize()
+    for g_, w_ in zip(got, want):
+        assert torch.equal(g_, w_)
+    assert _kernel_status() == 0
