@@ -184,9 +184,6 @@ static int fwd_impl(const fm_attn_args* a, const BlockScore& bs, void* stream) {
   fill_kparams(a, &p, false);
   p.md.nblk_pad = fm_mask_nblk_pad(a->Sk, tn);
   if (bs.block_logit) {
-    FM_REQUIRE(fwd_uses_sm100(a->d, a->dv) && fwd_sm100_supported(a), FM_ERR_UNSUPPORTED,
-               "fm_fwd_block_score: only the tcgen05 forward (head dims <= 128, 16-byte aligned q/k/v) "
-               "writes block scores (d=%d, dv=%d)", a->d, a->dv);
     FM_REQUIRE(bs.block_size == 32 || bs.block_size == 64 || bs.block_size == 128, FM_ERR_UNSUPPORTED,
                "fm_fwd_block_score: block_size must be 32, 64 or 128 (got %d)", bs.block_size);
     p.block_cols = (a->Sk + bs.block_size - 1) / bs.block_size;
@@ -195,7 +192,11 @@ static int fwd_impl(const fm_attn_args* a, const BlockScore& bs, void* stream) {
                bs.block_ld, p.block_cols);
     p.block_logit = bs.block_logit; p.block_bos = bs.block_bos; p.block_ld = bs.block_ld;
     p.block_log2 = bs.block_size == 32 ? 5 : (bs.block_size == 64 ? 6 : 7);
-    return fwd_sm100_launch(p, a, (cudaStream_t)stream);
+    // the tcgen05 kernels have compile-time variants for it; the warp-MMA kernels (head dims above 128,
+    // or FLASHMASK_B200_FWD=mma) a run-time branch
+    if (fwd_uses_sm100(a->d, a->dv) && fwd_sm100_supported(a)) return fwd_sm100_launch(p, a, (cudaStream_t)stream);
+    FM_REQUIRE(!fwd_uses_sm100(a->d, a->dv), FM_ERR_INVALID_ARGUMENT, "fm_fwd_block_score: q/k/v must be 16-byte aligned");
+    return fwd_mma_launch(p, a->dtype, (cudaStream_t)stream);
   }
   if (fwd_uses_sm100(a->d, a->dv) && fwd_sm100_supported(a)) {
     // with a launch table (a mask tensor) the persistent variant can walk it (FLASHMASK_B200_FWD_PERSIST=1);

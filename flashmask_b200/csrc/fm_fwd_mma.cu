@@ -154,6 +154,40 @@ fwd_mma_kernel(const AttnKParams p) {
       }
     }
 
+    // ---- optional block-score side output ---------------------------------
+    // Per (row, block of key columns) maximum of the masked, scaled scores, merged into
+    // block_logit with fmax (reference: flashmask/cute/flash_fwd_sm100.py:4256-4371).  A quad of
+    // lanes shares two rows; its lane 0 owns them in every tile, so the merge needs no atomics.
+    // One warp per row slab writes (the others hold the same scores).
+    if (p.block_logit != nullptr && ws == 0) {
+      constexpr int NSLOT = BC / 32 + 1;     // blocks a tile can touch at the smallest block size
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int row = r0 + r * 8;
+        const int bos = p.block_bos ? p.block_bos[(int64_t)b * p.Sq + min(row, p.Sq - 1)] : 0;
+        const int rel0 = j0 - bos;
+        const int base = rel0 >> p.block_log2;               // arithmetic shift: floor
+        float* dst = p.block_logit + (((int64_t)b * p.Hq + hq) * p.Sq + row) * p.block_ld;
+#pragma unroll
+        for (int k = 0; k < NSLOT; ++k) {
+          const int blk = base + k;
+          float mx = -INFINITY;
+#pragma unroll
+          for (int i = 0; i < NT_S; ++i) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int cl = i * 8 + tq * 2 + e;
+              if (((rel0 + cl) >> p.block_log2) == blk) mx = fmaxf(mx, s[i][2 * r + e]);
+            }
+          }
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+          // the scores are in log2 units here: back to softmax_scale * q.k
+          if (tq == 0 && row < p.Sq && blk >= 0 && blk < p.block_cols) dst[blk] = fmaxf(dst[blk], mx * kLn2);
+        }
+      }
+    }
+
     // ---- online softmax ---------------------------------------------------
 #pragma unroll
     for (int r = 0; r < 2; ++r) {

@@ -90,8 +90,8 @@ def _launch_order(a: "_lib.AttnArgs", info: FlashMaskInfo, which: int, ref: torc
     sel = os.environ.get("FLASHMASK_B200_ORDER", "1")
     names = ("fwd", "dq", "dkdv")
     wanted = [w for w in range(3) if sel == "1" or names[w] in sel.split(",")]
-    if which not in wanted:
-        return None
+    if which not in wanted or info.tile_n != 128:
+        return None     # the tables are counted in the 128-column tiles of the tcgen05 kernels, which alone read them
     geom = (a.d, a.dv, a.Sq, a.B, a.Hq, a.Hkv)
     if (which,) + geom not in info.orders:
         lib = _lib.load()

@@ -167,7 +167,7 @@ FM_API int fm_fwd(const fm_attn_args* args, void* stream);
  * ids are relative to that column: block j of a row covers the columns
  * [bos + j * block_size, bos + (j + 1) * block_size); NULL means bos = 0.
  * block_size is 32, 64 or 128; block_ld >= ceil(Sk / block_size); O and LSE
- * are bitwise those of fm_fwd.  FM_ERR_UNSUPPORTED for head dims above 128.
+ * are bitwise those of fm_fwd.  Every head dim fm_fwd takes is served.
  * Replaces the block_logit / block_size / block_bos arguments of
  * _flash_attn_fwd (flashmask/cute/ops/fwd.py:75-77,605-658) and the fused
  * epilogue of flashmask/cute/flash_fwd_sm100.py:4256-4371. */

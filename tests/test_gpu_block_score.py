@@ -49,18 +49,37 @@ def _check(got, ref, d, scale=None):
         assert diff <= 0.06 * math.sqrt(d) * scale, diff
 
 
+@pytest.fixture(params=["sm100", "mma"])
+def variant(request, monkeypatch):
+    """Head dims up to 128 have two forward kernel families, both with the side output."""
+    monkeypatch.setenv("FLASHMASK_B200_FWD", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("b,s,sk,h,d", [(1, 256, 256, 8, 64), (2, 512, 512, 4, 128), (2, 640, 640, 6, 128),
                                         (1, 384, 384, 2, 96)])
-def test_block_logit_shapes(b, s, sk, h, d, causal):
+def test_block_logit_shapes(b, s, sk, h, d, causal, variant):
     q, k, v = _inputs(b, s, sk, h, h, d, d, 0)
     _, _, bl = _run(q, k, v, causal, 64)
     _check(bl, oracle.block_logit_ref(q, k, None, causal, None, 64), d)
 
 
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("b,s,sk,h,d,dv", [(1, 512, 512, 8, 256, 256), (1, 1024, 1024, 2, 256, 256),
+                                           (1, 511, 513, 2, 256, 256), (1, 320, 320, 4, 192, 128)])
+def test_block_logit_head_dims_above_128(b, s, sk, h, d, dv, causal):
+    """Served by the warp-MMA forward (d = 256 is the reference's HySparse full-attention configuration)."""
+    q, k, v = _inputs(b, s, sk, h, h, d, dv, 11)
+    o0, l0 = fm._flash_attn_fwd(q.cuda(), k.cuda(), v.cuda(), causal=causal)
+    o1, l1, bl = _run(q, k, v, causal, 64)
+    assert torch.equal(o0, o1) and torch.equal(l0, l1)
+    _check(bl, oracle.block_logit_ref(q, k, None, causal, None, 64), d)
+
+
 @pytest.mark.parametrize("block_size", [32, 64, 128])
 @pytest.mark.parametrize("causal", [True, False])
-def test_block_logit_block_sizes(block_size, causal):
+def test_block_logit_block_sizes(block_size, causal, variant):
     q, k, v = _inputs(1, 512, 512, 4, 4, 128, 128, 1)
     _, _, bl = _run(q, k, v, causal, block_size)
     assert tuple(bl.shape) == (1, 4, 512, 512 // block_size)
@@ -109,11 +128,6 @@ def test_block_logit_rejects_pack_gqa_and_bad_arguments():
     with pytest.raises(NotImplementedError, match="block_size must be 32, 64 or 128"):
         fm._flash_attn_fwd(q.cuda(), k.cuda(), v.cuda(),
                            block_logit=torch.full((1, 8, 128, 8), NEG_INF, device="cuda"), block_size=16)
-    # head dims above 128 run on the warp-MMA kernels, which have no block-score epilogue
-    q2, k2, v2 = _inputs(1, 128, 128, 2, 2, 256, 256, 6)
-    with pytest.raises(NotImplementedError, match="only the tcgen05 forward"):
-        fm._flash_attn_fwd(q2.cuda(), k2.cuda(), v2.cuda(),
-                           block_logit=torch.full((1, 2, 128, 2), NEG_INF, device="cuda"))
 
 
 @pytest.mark.parametrize("block_size", [32, 64, 128])
@@ -126,7 +140,7 @@ def test_block_logit_large_multitile_noncausal(block_size):
     assert (bl.cpu() - ref).abs().max().item() <= 0.06
 
 
-def test_block_logit_unvisited_future_blocks_untouched_causal():
+def test_block_logit_unvisited_future_blocks_untouched_causal(variant):
     """Only visited K tiles are written: under causal the future tiles keep the caller's fill."""
     q, k, v = _inputs(1, 512, 512, 2, 2, 128, 128, 8)
     _, _, bl_inf = _run(q, k, v, True, 64)
@@ -153,7 +167,7 @@ def _doc_mask(B, S, cuts):
 
 @pytest.mark.parametrize("block_size", [32, 64, 128])
 @pytest.mark.parametrize("with_bos", [False, True])
-def test_block_logit_with_column_bound_mask(block_size, with_bos):
+def test_block_logit_with_column_bound_mask(block_size, with_bos, variant):
     """The block maxima see the attention's own mask; with block_bos the ids are document-relative
     (documents start at columns that are multiples of nothing: every straddling case occurs)."""
     B, S = 2, 1000
