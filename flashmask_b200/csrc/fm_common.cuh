@@ -252,6 +252,11 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
 }
 
+// Bits [0, x) of a 32-bit word set (x <= 0: none, x >= 32: all).
+__device__ __forceinline__ uint32_t bits_below(int x) {
+  return __funnelshift_lc(0xffffffffu, 0u, (uint32_t)max(x, 0));
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
