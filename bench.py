@@ -380,7 +380,7 @@ def main():
     peak_src = "measured (sustained cuBLAS bf16)" if peaks else "fallback"
     dom = "bwd" if ms_bwd >= ms_fwd else "fwd"
     # DRAM bytes per launch of this workload from one ncu capture (backward = preprocess + dK/dV + dQ kernels)
-    NCU_DRAM_BYTES = {"fwd": 392.2e6, "bwd": 1846.3e6}
+    NCU_DRAM_BYTES = {"fwd": 392.2e6, "bwd": 1771.0e6}
     dom_flops, dom_ms = (bwd_flops, ms_bwd) if dom == "bwd" else (fwd_flops, ms_fwd)
     ach = dom_flops / (dom_ms * 1e-3) / 1e12
     roofline = {"bound": "tensor", "kernel": "fm_bwd (preprocess + dK/dV + dQ kernels)" if dom == "bwd" else "fm_fwd kernel",
