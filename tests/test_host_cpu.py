@@ -45,6 +45,8 @@ def test_argument_errors_need_no_gpu():
     assert rc == 1 and b"ncols" in lib.fm_last_error()
     a = _lib.AttnArgs()
     assert lib.fm_fwd(ctypes.byref(a), None) == 1
+    assert lib.fm_fwd_block_score(ctypes.byref(a), None, 64, 1, None, None) == 1
+    assert b"block_logit is NULL" in lib.fm_last_error()
     with pytest.raises(NotImplementedError):
         fm.fwd_tile_shape(100, 300)
     with pytest.raises(RuntimeError):
