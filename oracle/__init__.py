@@ -16,6 +16,6 @@ stored vector of the reference ("parity unpinned" for those three: the
 restatements here are the pins).
 """
 from .attention import (dense_bias, attention_forward, attention_forward_backward,  # noqa: F401
-                        block_logit_ref)
+                        block_logit_ref, visible_block, candidate_columns, attention_rows, attention_columns)
 from .tiles import (nblk_pad, scan_max_min, valid_block_count, classify_tiles,  # noqa: F401
                     TILE_SKIP, TILE_PARTIAL, TILE_FULL)

@@ -171,3 +171,142 @@ def block_logit_ref(q, k, idx=None, causal=False, softmax_scale=None, block_size
     src = torch.where(ok[:, None].expand(B, Hq, Sq, Sk), scores, torch.full_like(scores, float("-inf")))
     out.scatter_reduce_(3, blk, src, reduce="amax", include_self=True)
     return out
+
+
+# ---------------------------------------------------------------------------
+# The same mathematics for ONE (batch, head) on a subset of query rows or key columns, so that
+# the benchmark configurations can be checked at their full sequence lengths (8K-128K tokens),
+# where a dense [Sq, Sk] score matrix of every head no longer fits the checker's memory or time.
+# ---------------------------------------------------------------------------
+def visible_block(bounds: Optional[np.ndarray], Sq: int, Sk: int, causal: bool,
+                  rows: np.ndarray, cols: np.ndarray) -> np.ndarray:
+    """bool [len(rows), len(cols)]: element (row, col) is unmasked.  ``bounds`` is the mask of one
+    (batch, mask head), ``[Sk, ncols]`` int, or None.  Same predicate as ``dense_bias`` (restating
+    tests/common/startend_row_indices.py:188-222), evaluated for the given global row / column
+    indices only."""
+    i = np.asarray(rows, dtype=np.int64)[:, None]
+    j = np.asarray(cols, dtype=np.int64)[None, :]
+    masked = np.zeros((i.shape[0], j.shape[1]), dtype=bool)
+    if bounds is not None:
+        a = np.asarray(bounds)[np.asarray(cols)].astype(np.int64)       # [C, n]
+        n = a.shape[1]
+        has_end = (causal and n == 2) or ((not causal) and n == 4)
+        masked = ((i >= a[:, 0]) & (i < a[:, 1])) if has_end else (i >= a[:, 0])
+        if not causal:
+            masked = masked | (((i >= a[:, 2]) & (i < a[:, 3])) if has_end else (i < a[:, 1]))
+    if causal:
+        masked = masked | (j > i + (Sk - Sq))
+    return ~masked
+
+
+def candidate_columns(bounds: Optional[np.ndarray], Sq: int, Sk: int, causal: bool,
+                      rmin: int, rmax: int) -> np.ndarray:
+    """Key columns that are not masked for EVERY row of [rmin, rmax] (a superset of the columns
+    some row of that range sees), from the bounds alone in O(Sk): a column is dropped when one of
+    its masked row intervals covers the whole range, or when it lies in the causal future of rmax."""
+    j = np.arange(Sk, dtype=np.int64)
+    drop = np.zeros(Sk, dtype=bool)
+    if bounds is not None:
+        a = np.asarray(bounds).astype(np.int64)
+        n = a.shape[1]
+        has_end = (causal and n == 2) or ((not causal) and n == 4)
+        drop = (a[:, 0] <= rmin) & ((a[:, 1] > rmax) if has_end else True)
+        if not causal:
+            drop = drop | (((a[:, 2] <= rmin) & (a[:, 3] > rmax)) if has_end else (a[:, 1] > rmax))
+    if causal:
+        drop = drop | (j > rmax + (Sk - Sq))
+    return np.nonzero(~drop)[0]
+
+
+def attention_rows(q, k, v, d_out, bounds, causal, sink=None, softmax_scale=None, rows=None,
+                   chunk=1024, grads=True):
+    """fp32 attention of ONE head restricted to the query rows ``rows`` (all rows when None).
+
+    q ``[Sq, d]``, k ``[Sk, d]``, v ``[Sk, dv]``, d_out ``[Sq, dv]`` (torch CPU), ``bounds``
+    ``[Sk, ncols]`` numpy or None, ``sink`` a python float or None.  Returns a dict with, for the
+    selected rows in order, ``out [R, dv]``, ``lse [R]``, ``dpsum [R]``, ``dq [R, d]`` and the
+    contribution of those rows to ``dk [Sk, d]`` / ``dv [Sk, dv]`` (the full gradient of this head
+    when every row is selected).  Same formulas as ``attention_forward_backward``; rows are walked in
+    chunks and each chunk only touches the key columns at least one of its rows can see."""
+    q = q.to(torch.float32); k = k.to(torch.float32); v = v.to(torch.float32)
+    do = d_out.to(torch.float32) if d_out is not None else None
+    Sq, d = q.shape
+    Sk, dv = v.shape
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
+    rows = np.arange(Sq, dtype=np.int64) if rows is None else np.asarray(rows, dtype=np.int64)
+    R = rows.shape[0]
+    res = dict(out=torch.zeros(R, dv), lse=torch.full((R,), float("-inf")), dpsum=torch.zeros(R))
+    if grads:
+        res.update(dq=torch.zeros(R, d), dk=torch.zeros(Sk, d), dv=torch.zeros(Sk, dv))
+    for c0 in range(0, R, chunk):
+        rr = rows[c0:c0 + chunk]
+        cand = candidate_columns(bounds, Sq, Sk, causal, int(rr.min()), int(rr.max()))
+        vis_np = visible_block(bounds, Sq, Sk, causal, rr, cand)
+        keep = vis_np.any(axis=0)
+        cols = cand[keep]
+        sl = slice(c0, c0 + rr.shape[0])
+        if sink is not None:
+            res["lse"][sl] = float(sink)
+        if cols.size == 0:
+            continue
+        vis = torch.from_numpy(vis_np[:, keep])
+        ct = torch.from_numpy(cols)
+        rt = torch.from_numpy(rr)
+        kc, vc = k[ct], v[ct]
+        s = torch.matmul(q[rt] * scale, kc.T)
+        s = torch.where(vis, s, torch.full_like(s, float("-inf")))
+        full = s if sink is None else torch.cat([s, torch.full((rr.shape[0], 1), float(sink))], dim=1)
+        lse = torch.logsumexp(full, dim=-1)
+        safe = torch.where(torch.isinf(lse) & (lse < 0), torch.zeros_like(lse), lse)
+        P = torch.where(vis, torch.exp(s - safe[:, None]), torch.zeros_like(s))
+        out = torch.matmul(P, vc)
+        res["out"][sl] = out
+        res["lse"][sl] = lse
+        if do is None:
+            continue
+        dor = do[rt]
+        dpsum = (out * dor).sum(-1)
+        res["dpsum"][sl] = dpsum
+        if not grads:
+            continue
+        dP = torch.matmul(dor, vc.T)
+        dS = P * (dP - dpsum[:, None])
+        res["dq"][sl] = torch.matmul(dS, kc) * scale
+        res["dk"].index_add_(0, ct, torch.matmul(dS.T, q[rt]) * scale)
+        res["dv"].index_add_(0, ct, torch.matmul(P.T, dor))
+    return res
+
+
+def attention_columns(q, k_cols, v_cols, d_out, lse, dpsum, bounds, causal, cols, Sk,
+                      softmax_scale=None, chunk=2048):
+    """fp32 dK / dV of the key columns ``cols`` of ONE kv head: ``dk [C, d]``, ``dv [C, dv]``.
+
+    q ``[G, Sq, d]`` and d_out ``[G, Sq, dv]`` are the q heads of the kv head's group; ``lse`` and
+    ``dpsum`` ``[G, Sq]`` their row statistics (natural-log LSE, rowsum(O * dO)); ``k_cols`` /
+    ``v_cols`` the selected rows of k / v.  dV = P^T dO and dK = scale * dS^T Q summed over the
+    group (flashmask/cute/flash_bwd_sm100.py:129-140), with P = exp(S - LSE) from the given LSE."""
+    q = q.to(torch.float32); do = d_out.to(torch.float32)
+    kc = k_cols.to(torch.float32); vc = v_cols.to(torch.float32)
+    lse = lse.to(torch.float32); dpsum = dpsum.to(torch.float32)
+    G, Sq, d = q.shape
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
+    cols = np.asarray(cols, dtype=np.int64)
+    dk = torch.zeros(cols.shape[0], d)
+    dvv = torch.zeros(cols.shape[0], vc.shape[1])
+    for r0 in range(0, Sq, chunk):
+        rr = np.arange(r0, min(r0 + chunk, Sq), dtype=np.int64)
+        vis_np = visible_block(bounds, Sq, Sk, causal, rr, cols)
+        if not vis_np.any():
+            continue
+        vis = torch.from_numpy(vis_np)
+        for g in range(G):
+            l = lse[g, r0:r0 + rr.shape[0]]
+            dead = torch.isinf(l)
+            s = torch.matmul(q[g, r0:r0 + rr.shape[0]] * scale, kc.T)
+            P = torch.exp(s - torch.where(dead, torch.zeros_like(l), l)[:, None])
+            P = torch.where(vis & ~dead[:, None], P, torch.zeros_like(P))
+            dor = do[g, r0:r0 + rr.shape[0]]
+            dS = P * (torch.matmul(dor, vc.T) - dpsum[g, r0:r0 + rr.shape[0]][:, None])
+            dk += torch.matmul(dS.T, q[g, r0:r0 + rr.shape[0]]) * scale
+            dvv += torch.matmul(P.T, dor)
+    return dk, dvv

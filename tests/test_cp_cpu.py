@@ -38,6 +38,27 @@ def test_heap_known_answer():
     assert sum(weights) == 355 and max(weights) <= 180
 
 
+def test_heap_partition_matches_reference_vectors():
+    """fm_cp_partition_heap and the restatement against assignments computed by the reference's own
+    assign_tasks_heap (tests/golden/make_heap_golden.py lifts the function out of
+    flashmask/cp_balance/cp_balance.py:96-174 and runs it)."""
+    z = np.load(os.path.join(ROOT, "tests", "golden", "heap_partition.npz"))
+    n_cases = int(z["n_cases"])
+    assert n_cases >= 72
+    for k in range(n_cases):
+        w, m, want = z[f"w_{k}"], int(z[f"m_{k}"]), z[f"b_{k}"]
+        tasks = np.stack([w, np.arange(len(w))], axis=1).astype(np.int32)
+        for impl in (cp_balance.assign_tasks_heap, ocp.assign_tasks_heap):
+            buckets, bw, cuts = impl(tasks, m)
+            got = np.full(len(w), -1, dtype=np.int32)
+            for r, items in enumerate(buckets):
+                assert [i for _, i in items] == sorted(i for _, i in items)
+                got[[int(i) for _, i in items]] = r
+            assert np.array_equal(got, want), (k, impl.__module__)
+            assert [int(x) for x in bw] == [int(x) for x in z[f"bw_{k}"]]
+            assert int(cuts) == int(z[f"cuts_{k}"])
+
+
 def test_reference_ipo_solver_oracle_if_built():
     """oracle/_ref/libcpsolver_ref.so is the reference's own IPO solver header; the
     heap partition may never beat it and must stay within 4/3 of it (LPT bound)."""

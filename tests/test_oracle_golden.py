@@ -97,3 +97,50 @@ def test_block_logit_restatement_matches_the_reference_checker_formula():
             lo, hi = int(bos[b, r]) + blk * bs, min(int(bos[b, r]) + (blk + 1) * bs, Sk)
             w = s[b, h, r, lo:hi].max().item() if lo < hi else float("-inf")
             assert got[b, h, r, blk].item() == pytest.approx(w, abs=1e-6) or (w == float("-inf") and got[b, h, r, blk].item() == w)
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=lambda p: os.path.basename(p)[10:-4])
+def test_row_and_column_restrictions_agree_with_the_pinned_oracle(path):
+    """attention_rows / attention_columns (the checker of the full-size configurations) against
+    attention_forward_backward, which the golden vectors above pin: every row, a sample of rows,
+    and a sample of key columns of one head group."""
+    c = _case(path)
+    idx = c.get("idx")
+    causal = bool(c["causal"])
+    q, k, v, do = (torch.from_numpy(c[n]) for n in ("q", "k", "v", "do"))
+    sink = torch.from_numpy(c["sink"]) if "sink" in c else None
+    B, Sq, Hq, d = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    G = Hq // Hkv
+    full = oracle.attention_forward_backward(q, k, v, do, idx, causal, sink)
+    b, hk = B - 1, Hkv - 1
+    bounds = None if idx is None else idx[b if idx.shape[0] > 1 else 0, hk if idx.shape[1] > 1 else 0]
+    rng = np.random.default_rng(0)
+    some = np.unique(np.concatenate([[0, Sq - 1], rng.choice(Sq, min(Sq, 9), replace=False)]))
+    dk = torch.zeros(Sk, d); dvv = torch.zeros(Sk, v.shape[3])
+    lse_g, dps_g = [], []
+    for g in range(G):
+        h = hk * G + g
+        s = None if sink is None else float(sink[h])
+        r = oracle.attention_rows(q[b, :, h], k[b, :, hk], v[b, :, hk], do[b, :, h], bounds, causal, s,
+                                  chunk=7)
+        for name in ("out", "dq"):
+            torch.testing.assert_close(r[name], full[name][b, :, h], rtol=2e-5, atol=2e-6)
+        assert torch.equal(torch.isinf(r["lse"]), torch.isinf(full["lse"][b, h]))
+        fin = torch.isfinite(r["lse"])
+        torch.testing.assert_close(r["lse"][fin], full["lse"][b, h][fin], rtol=2e-5, atol=2e-6)
+        dk += r["dk"]; dvv += r["dv"]
+        lse_g.append(r["lse"]); dps_g.append(r["dpsum"])
+        part = oracle.attention_rows(q[b, :, h], k[b, :, hk], v[b, :, hk], do[b, :, h], bounds, causal, s,
+                                     rows=some, chunk=4)
+        torch.testing.assert_close(part["out"], full["out"][b, some, h], rtol=2e-5, atol=2e-6)
+        torch.testing.assert_close(part["dq"], full["dq"][b, some, h], rtol=2e-5, atol=2e-6)
+    torch.testing.assert_close(dk, full["dk"][b, :, hk], rtol=2e-5, atol=4e-6)
+    torch.testing.assert_close(dvv, full["dv"][b, :, hk], rtol=2e-5, atol=4e-6)
+    cols = np.unique(np.concatenate([[0, Sk - 1], rng.choice(Sk, min(Sk, 11), replace=False)]))
+    hs = slice(hk * G, hk * G + G)
+    ck, cv = oracle.attention_columns(q[b, :, hs].permute(1, 0, 2), k[b, cols, hk], v[b, cols, hk],
+                                      do[b, :, hs].permute(1, 0, 2), torch.stack(lse_g), torch.stack(dps_g),
+                                      bounds, causal, cols, Sk, chunk=5)
+    torch.testing.assert_close(ck, full["dk"][b, cols, hk], rtol=2e-5, atol=4e-6)
+    torch.testing.assert_close(cv, full["dv"][b, cols, hk], rtol=2e-5, atol=4e-6)
