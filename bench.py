@@ -104,9 +104,30 @@ class ClockSampler:
 # ---------------------------------------------------------------------------
 def cpu_sample(w, heads: int = 4):
     """Bounded sample of the workload for the CPU arm: batch 0, one kv head and
-    the first ``heads`` q heads of its group, the full sequence."""
+    the first ``heads`` q heads of its group; the full sequence up to 16K tokens, a
+    sample of 1024 query rows (forward, dQ and their share of dK / dV) beyond."""
     import oracle  # CPU-baseline leg only
     g = torch.Generator().manual_seed(w.seed)
+    heads = min(heads, w.Hq // w.Hkv)
+    if w.Sq > 16384:
+        q = torch.randn(w.Sq, heads, w.d, generator=g)
+        k = torch.randn(w.Sk, w.d, generator=g)
+        v = torch.randn(w.Sk, w.dv, generator=g)
+        do = torch.randn(w.Sq, heads, w.dv, generator=g)
+        bounds = None if w.idx is None else w.idx[0, 0]
+        rows = np.sort(np.random.default_rng(w.seed).choice(w.Sq, 1024, replace=False))
+        nvis = 0
+        for c0 in range(0, rows.size, 512):
+            nvis += int(oracle.visible_block(bounds, w.Sq, w.Sk, w.causal, rows[c0:c0 + 512],
+                                             np.arange(w.Sk)).sum())
+        flops = 2 * nvis * heads * (4 * w.d + 3 * w.dv)
+
+        def step_rows():
+            return [oracle.attention_rows(q[:, h], k, v, do[:, h], bounds, w.causal, rows=rows)
+                    for h in range(heads)]
+        desc = (f"batch 0, 1 kv head x {heads} q heads, 1024 sampled query rows of S={w.Sq} against all keys "
+                f"({nvis * heads / max(1, w.n_visible()):.2e} of the workload's unmasked pairs), fp32")
+        return step_rows, flops, desc
     q = torch.randn(1, w.Sq, heads, w.d, generator=g)
     k = torch.randn(1, w.Sk, 1, w.d, generator=g)
     v = torch.randn(1, w.Sk, 1, w.dv, generator=g)
@@ -149,6 +170,13 @@ def run_cp(args, rank, local_rank, world):
     name = args.workload or "cp_causal_doc_128k"
     w = W.make_workload(name)
     chunk = 2048
+    from flashmask_b200 import _lib
+    parity = cp_parity_check(name, rank, world, dev, chunk)
+    if not parity["ok"]:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "n_gpus": world, "cp_parity": parity, "error": "cp parity failed"}))
+        dist.destroy_process_group()
+        sys.exit(1)
     idx = torch.from_numpy(w.idx).to(dev)
     t0 = time.perf_counter()
     local_mask, buckets = cp_balance.balance_flashmask_input(idx, world, rank, balance_chunk_size=chunk)
@@ -185,16 +213,32 @@ def run_cp(args, rank, local_rank, world):
     ins = [fresh() for _ in range(args.steps)]
     barrier()
     sampler.mark()
+    n0 = _lib.load().fm_launch_count()
     e0.record()
     for i in range(args.steps):
         step(*ins[i])
     e1.record()
+    launches = torch.tensor([_lib.load().fm_launch_count() - n0], device=dev, dtype=torch.int64)
     barrier()
     clocks = sampler.stop()
     t = torch.tensor([e0.elapsed_time(e1)], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dist.all_reduce(launches, op=dist.ReduceOp.SUM)
     ms_step = t.item() / args.steps
     value = (fwd_flops + bwd_flops) / (ms_step * 1e-3) / 1e12
+    phases = None
+    if args.cp_phases:
+        from flashmask_b200 import cp as cpm
+        cpm.profile_phases(True)
+        for _ in range(3):
+            step(*fresh())
+        rep = cpm.phase_report()
+        cpm.profile_phases(False)
+        names = sorted(rep)
+        vals = torch.tensor([rep[n_] / 3 for n_ in names], device=dev)
+        allv = [torch.empty_like(vals) for _ in range(world)]
+        dist.all_gather(allv, vals)
+        phases = {n_: [round(float(a_[i]), 3) for a_ in allv] for i, n_ in enumerate(names)}
 
     e2e = None
     if not args.no_e2e:
@@ -237,15 +281,51 @@ def run_cp(args, rank, local_rank, world):
                        "l2": "per-rank tensors exceed the 126 MB L2; no flush between steps",
                        "mask_sparsity": round(w.sparsity(), 4), "parallelism": f"cp{world}",
                        "partition_ms": partition_ms, "rank_loads": loads},
-            "clocks": clocks, "e2e": e2e,
-            "gpu_launches": args.steps * 20, "tokens_per_s": w.B * w.Sq / (ms_step * 1e-3),
+            "clocks": clocks, "e2e": e2e, "cp_parity": parity,
+            "gpu_launches": int(launches.item()), "tokens_per_s": w.B * w.Sq / (ms_step * 1e-3),
             "roofline": {"bound": "tensor", "kernel": "fwd + bwd tcgen05 kernels over all ring steps (aggregate)",
                          "achieved": value / world, "peak": peak_tf, "unit": "TFLOP/s",
                          "frac": value / world / peak_tf, "peak_source": "measured (sustained cuBLAS bf16)",
                          "traffic": None}}
+    if phases is not None:
+        line["cp_phases_ms_per_rank"] = phases
     if rank == 0:
         print(json.dumps(line))
     dist.destroy_process_group()
+
+
+def cp_parity_check(name, rank, world, dev, chunk, S=16384):
+    """Before anything is timed: the context-parallel operator on a reduced copy of the workload
+    (same generator, S tokens) against the single-GPU operator, on this rank's rows and keys.
+    Returns {"ok", "max_err", "tol", "S"} with the maximum over ranks and over out / dq / dk / dv
+    (tolerance: every element is a sum of at most `world` bf16-rounded partials)."""
+    import torch.distributed as dist
+    import flashmask_b200 as fm
+    from flashmask_b200 import cp_balance, workloads as W
+    w = W.make_workload(name, S=S)
+    idx = torch.from_numpy(w.idx).to(dev)
+    g = torch.Generator().manual_seed(w.seed)
+    q, k, v, do = (torch.randn(w.B, S, h, dd, generator=g).to(torch.bfloat16).to(dev)
+                   for h, dd in ((w.Hq, w.d), (w.Hkv, w.d), (w.Hkv, w.dv), (w.Hq, w.dv)))
+    local, buckets = cp_balance.balance_flashmask_input(idx, world, rank, balance_chunk_size=chunk)
+    ql, kl, vl, dol = (cp_balance.scatter_by_buckets(t, buckets, rank) for t in (q, k, v, do))
+    ql, kl, vl = (t.requires_grad_(True) for t in (ql, kl, vl))
+    out = fm.flashmask_attention(ql, kl, vl, local, causal=False, group=dist.group.WORLD, deterministic=True)
+    out.backward(dol)
+    qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+    ref = fm.flashmask_attention(qg, kg, vg, idx, causal=False, deterministic=True)
+    ref.backward(do)
+    worst, ok = 0.0, True
+    for a, b in ((out, ref), (ql.grad, qg.grad), (kl.grad, kg.grad), (vl.grad, vg.grad)):
+        bl = cp_balance.scatter_by_buckets(b.detach(), buckets, rank).float()
+        err = (a.detach().float() - bl).abs().max().item()
+        tol = 2 ** -7 * world * max(1.0, bl.abs().max().item())
+        worst = max(worst, err / tol)
+        ok = ok and err <= tol and not torch.isnan(a.float()).any().item()
+    t = torch.tensor([worst, 0.0 if ok else 1.0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {"ok": t[1].item() == 0.0, "max_err_over_tol": round(t[0].item(), 4), "S": S,
+            "checked": "out, dq, dk, dv of every rank vs the single-GPU operator, bf16"}
 
 
 # ---------------------------------------------------------------------------
@@ -258,19 +338,24 @@ def main():
     ap.add_argument("--workload", default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--cp-phases", action="store_true", help="N > 1: per-phase device times of every rank")
+    ap.add_argument("--sustained", type=float, default=2.0,
+                    help="N = 1: seconds of back-to-back steps for the sustained-clock figure (0: skip)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     from flashmask_b200 import workloads as W
-    name = args.workload or "causal_doc_8k_gqa"
+    name = args.workload or ("cp_causal_doc_128k" if args.gpus > 1 else "causal_doc_8k_gqa")
     w = W.make_workload(name)
+    kind = ("causal mask, per-head sink logit, deterministic backward" if w.idx is None else
+            "mask from the column bounds of the named workload")
     config = {"workload": f"{name}: B={w.B} Hq={w.Hq} Hkv={w.Hkv} S={w.Sq} d={w.d} dv={w.dv} "
-                          f"causal-document mask (lognormal doc lengths), bf16, fwd+bwd",
+                          f"{kind}, bf16, fwd+bwd",
               "l2": "inputs+outputs (>500 MB) exceed the 126 MB L2; no flush between steps",
               "mask_sparsity": round(w.sparsity(), 4),
-              "parallelism": "1 GPU" if world == 1 else f"{world} independent replicas"}
+              "parallelism": "1 GPU" if args.gpus == 1 else f"cp{args.gpus}"}
 
     if args.impl == "reference":
         if rank != 0:
@@ -281,8 +366,8 @@ def main():
         val, ms = time_cpu(step, flops, max(1, args.steps), max(1, args.warmup))
         line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": config,
+                "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "config": config,
                 "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
                 "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
@@ -293,8 +378,10 @@ def main():
         return run_cp(args, rank, local_rank, world)
 
     import flashmask_b200 as fm
+    from flashmask_b200 import _lib
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    launch_count = _lib.load().fm_launch_count
 
     g = torch.Generator().manual_seed(w.seed + rank)
     host = {
@@ -307,25 +394,19 @@ def main():
     q, k, v, do = (host[n].to(dev) for n in ("q", "k", "v", "do"))
     idx = idx_host.to(dev) if idx_host is not None else None
     fwd_flops, bwd_flops = w.flops()
-    n_launch = {"fwd": 0, "bwd": 0}
+    sink = torch.randn(w.Hq, generator=g).to(dev) if w.sink else None
+    det = bool(w.deterministic)
 
     ftm, ftn = fm.fwd_tile_shape(w.d, w.dv)
     btm, btn = fm.bwd_tile_shape(w.d, w.dv)
 
     def step_device():
-        # mask preprocessing is part of every step (2 launches when fwd and bwd share tile_n)
+        # mask preprocessing and the launch tables are part of every step
         info_f = fm.prepare_mask(idx, w.Sq, w.causal, ftm, ftn) if idx is not None else None
         info_b = info_f if (info_f is None or btn == ftn) else fm.prepare_mask(idx, w.Sq, w.causal, btm, btn)
-        out, lse = fm._flash_attn_fwd(q, k, v, idx, causal=w.causal, mask_info=info_f)
-        res = fm._flash_attn_bwd(q, k, v, out, do, lse, idx, causal=w.causal, mask_info=info_b)
-        # launch tables are built once per mask info, i.e. once per step here (one launch for all three)
-        n_launch["order"] = sum(1 for i in {id(info_f): info_f, id(info_b): info_b}.values()
-                                if i is not None and any(t is not None for t in i.orders.values()))
-        return res
-
-    # mask scan (+1 if fwd and bwd tile widths differ) + launch-order tables + forward + (preprocess, dK/dV, dQ)
-    launches_per_step = lambda: ((1 if idx is not None else 0) * (1 if btn == ftn else 2) +
-                                 n_launch.get("order", 0) + 1 + 3)
+        out, lse = fm._flash_attn_fwd(q, k, v, idx, causal=w.causal, learnable_sink=sink, mask_info=info_f)
+        return fm._flash_attn_bwd(q, k, v, out, do, lse, idx, causal=w.causal, learnable_sink=sink,
+                                  deterministic=det, mask_info=info_b)
 
     def barrier():
         if world > 1:
@@ -339,13 +420,34 @@ def main():
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler.mark()
+    n0 = launch_count()
     e0.record()
     for _ in range(args.steps):
         step_device()
     e1.record()
+    gpu_launches = launch_count() - n0
     barrier()
     ms_total = e0.elapsed_time(e1)
     clocks = sampler.stop()
+    # the same step back to back for a few seconds: the clocks a long training run sees (power cap)
+    sustained = None
+    if args.sustained > 0 and world == 1:
+        n_s = max(args.steps, int(args.sustained * 1e3 / max(ms_total / args.steps, 1e-3)))
+        smp = ClockSampler(local_rank)
+        smp.start()
+        time.sleep(0.3)
+        torch.cuda.synchronize()
+        smp.mark()
+        a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a_.record()
+        for _ in range(n_s):
+            step_device()
+        b_.record()
+        torch.cuda.synchronize()
+        ck = smp.stop()
+        ms_s = a_.elapsed_time(b_) / n_s
+        sustained = {"steps": n_s, "ms_per_step": ms_s,
+                     "value": (fwd_flops + bwd_flops) / (ms_s * 1e-3) / 1e12, "unit": UNIT, "clocks": ck}
     t = torch.tensor([ms_total], device=dev)
     if world > 1:
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
@@ -355,7 +457,7 @@ def main():
     # per-kernel-group timing on the launching stream (roofline of the dominant one)
     info_f = fm.prepare_mask(idx, w.Sq, w.causal, ftm, ftn) if idx is not None else None
     info_b = info_f if (info_f is None or btn == ftn) else fm.prepare_mask(idx, w.Sq, w.causal, btm, btn)
-    out, lse = fm._flash_attn_fwd(q, k, v, idx, causal=w.causal, mask_info=info_f)
+    out, lse = fm._flash_attn_fwd(q, k, v, idx, causal=w.causal, learnable_sink=sink, mask_info=info_f)
 
     def timed(fn, reps):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -367,8 +469,10 @@ def main():
         torch.cuda.synchronize()
         return a.elapsed_time(b) / reps
     reps = max(3, args.steps // 2)
-    ms_fwd = timed(lambda: fm._flash_attn_fwd(q, k, v, idx, causal=w.causal, mask_info=info_f), reps)
-    ms_bwd = timed(lambda: fm._flash_attn_bwd(q, k, v, out, do, lse, idx, causal=w.causal, mask_info=info_b), reps)
+    ms_fwd = timed(lambda: fm._flash_attn_fwd(q, k, v, idx, causal=w.causal, learnable_sink=sink,
+                                              mask_info=info_f), reps)
+    ms_bwd = timed(lambda: fm._flash_attn_bwd(q, k, v, out, do, lse, idx, causal=w.causal, learnable_sink=sink,
+                                              deterministic=det, mask_info=info_b), reps)
     ms_prep = timed(lambda: fm.prepare_mask(idx, w.Sq, w.causal, ftm, ftn), reps) if idx is not None else 0.0
 
     peaks = {}
@@ -401,7 +505,7 @@ def main():
         vd = host["v"].to(dev, non_blocking=True).requires_grad_(True)
         dod = host["do"].to(dev, non_blocking=True)
         idd = idx_host.to(dev, non_blocking=True) if idx_host is not None else None
-        o = fm.flashmask_attention(qd, kd, vd, idd, causal=w.causal)
+        o = fm.flashmask_attention(qd, kd, vd, idd, causal=w.causal, sink=sink, deterministic=det)
         o.backward(dod)
         res["out"].copy_(o.detach(), non_blocking=True)
         res["dq"].copy_(qd.grad, non_blocking=True)
@@ -436,7 +540,7 @@ def main():
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": config, "clocks": clocks,
             "e2e": e2e,
-            "gpu_launches": launches_per_step() * args.steps, "roofline": roofline,
+            "gpu_launches": int(gpu_launches), "roofline": roofline, "sustained": sustained,
             "frac_of_peak_fwd_bwd": value / world / peak_tf,
             "tokens_per_s": world * w.B * w.Sq / (ms_step * 1e-3)}
     if w.Sq <= 16384:
@@ -459,6 +563,7 @@ def main():
         ms_c = timed(step_c, 5) if (step_c(), step_c(), step_c()) else 0.0
         fc, bc = wc.flops()
         line["cp_128k_single_gpu"] = {"ms_per_step": ms_c, "tokens_per_s": wc.B * wc.Sq / (ms_c * 1e-3),
+                                      "mask_form": "non-causal 2-column [LTS, UTE], as in the N > 1 runs",
                                       "value": (fc + bc) / (ms_c * 1e-3) / 1e12, "unit": UNIT,
                                       "mask_sparsity": round(wc.sparsity(), 4)}
         del qc, kc, vc, doc

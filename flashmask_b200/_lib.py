@@ -53,6 +53,8 @@ SIGNATURES = {
                                         C.c_int, C.c_void_p, C.c_void_p]),
     "fm_fwd_tile_shape": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "fm_bwd_tile_shape": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "fm_reload_options": (C.c_int, []),
+    "fm_launch_count": (C.c_ulonglong, []),
     "fm_fwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "fm_fwd_block_score": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "fm_launch_order_ints": (C.c_int64, [C.POINTER(AttnArgs), C.c_int]),
@@ -107,3 +109,9 @@ def check(rc: int, what: str) -> None:
         msg = load().fm_last_error().decode()
         cls = {1: ValueError, 2: NotImplementedError}.get(rc, RuntimeError)
         raise cls(f"{what} failed (status {rc}): {msg}")
+
+
+def reload_options() -> None:
+    """Have the library read its FLASHMASK_B200_* switches from the environment again (it reads
+    them once at load; nothing on the call path does)."""
+    check(load().fm_reload_options(), "fm_reload_options")

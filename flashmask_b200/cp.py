@@ -10,14 +10,15 @@ owner of each shard.
 
 Schedule (one NVSwitch domain, every peer at full bandwidth): a rank pulls the
 shards it needs straight from their owners with ONE grouped NCCL send/recv on a
-high-priority side stream, into one local K/V buffer that holds the other
-ranks' shards concatenated in rank order.  The forward is two attention calls
+high-priority side stream, into one local K/V buffer that holds the pulled
+shards concatenated in rank order of their owners.  The forward is two attention calls
 whatever the group size: local queries x own shard (overlaps with the
 exchange) and local queries x that remote buffer (one launch; tile skipping
-drops shards, or parts of shards, that nothing sees), merged by log-sum-exp in
+drops the parts of shards that nothing sees), merged by log-sum-exp in
 fp32.  A (rank, shard) pair whose part of the mask holds no visible element is
-not transferred at all; all ranks derive the same need matrix from one small
-all-gather.  The backward runs the remote call first, sends each owner the
+neither transferred nor given a place in the buffer; all ranks derive the same
+need matrix from one small all-gather, once per mask tensor (the split masks,
+their tile reductions and launch tables are kept with it).  The backward runs the remote call first, sends each owner the
 bf16 dK/dV slice of its shard while the own-shard call runs, and every owner
 sums the contributions in rank order in fp32 and rounds once: bitwise
 reproducible.  Remote data is only ever consumed from local HBM.
@@ -26,16 +27,56 @@ from __future__ import annotations
 
 import ctypes as C
 import math
-from dataclasses import dataclass
-from typing import Dict, List, Optional
+import weakref
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional
 
 import torch
 
 from . import _lib
-from .ops import _dtype_code, _flash_attn_bwd, _flash_attn_fwd, _stream
+from .ops import (FlashMaskInfo, _dtype_code, _flash_attn_bwd, _flash_attn_fwd, _stream, bwd_tile_shape,
+                  prepare_mask)
 
-__all__ = ["cp_flashmask_attention", "CPPlan", "TorchDistExchange", "RemoteKV", "build_plan", "cp_forward",
-           "emulate_cp", "shard_need_row"]
+__all__ = ["cp_flashmask_attention", "CPPlan", "CPMaskState", "TorchDistExchange", "RemoteKV", "mask_state",
+           "invalidate_mask_state", "cp_forward", "emulate_cp", "shard_need_row", "profile_phases",
+           "phase_report"]
+
+
+# ---------------------------------------------------------------------------
+# optional per-phase device timing (CUDA events on the compute stream)
+# ---------------------------------------------------------------------------
+_PHASES: Optional[list] = None
+
+
+def profile_phases(on: bool) -> None:
+    """Start (or stop and drop) the recording of phase marks: every phase boundary of the
+    context-parallel forward / backward records a CUDA event on the current stream."""
+    global _PHASES
+    _PHASES = [] if on else None
+
+
+def _mark(name: str) -> None:
+    if _PHASES is not None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        _PHASES.append((name, ev))
+
+
+def phase_report() -> Dict[str, float]:
+    """Milliseconds per phase since profile_phases(True), summed over calls: the time between a
+    mark and the one before it on the compute stream (idle time of the stream, e.g. waiting for
+    the host or for a transfer, counts towards the phase it precedes).  Clears the marks."""
+    global _PHASES
+    out: Dict[str, float] = {}
+    if not _PHASES:
+        return out
+    torch.cuda.synchronize()
+    for (n0, e0), (n1, e1) in zip(_PHASES[:-1], _PHASES[1:]):
+        if n1.endswith(":begin"):
+            continue
+        out[n1] = out.get(n1, 0.0) + e0.elapsed_time(e1)
+    _PHASES = []
+    return out
 
 
 # ---------------------------------------------------------------------------
@@ -56,6 +97,10 @@ class CPPlan:
         """Ranks that pull this rank's shard, in the order they ask for it."""
         return [t for s in range(1, self.world) for t in [(self.rank + s) % self.world]
                 if self.need[t][self.rank]]
+
+    def pull_order(self) -> List[int]:
+        """The pulled owners in rank order: the order of their shards in the remote K/V buffer."""
+        return sorted(self.pulls())
 
 
 def shard_need_row(local_mask: Optional[torch.Tensor], Sq: int, causal: bool, world: int) -> torch.Tensor:
@@ -155,38 +200,40 @@ def _reduce_partials(parts: List[torch.Tensor]) -> torch.Tensor:
 # per-rank forward / backward: two attention calls whatever the group size
 #   "own"    local queries x this rank's own K/V shard (needs no transfer and
 #            overlaps with the exchange)
-#   "remote" local queries x every other shard, concatenated in rank order in
+#   "remote" local queries x every pulled shard, concatenated in rank order in
 #            ONE K/V buffer with the matching mask columns: one launch, tile
-#            skipping takes care of shards (or parts of shards) nothing sees
+#            skipping takes care of the parts of shards nothing sees
 # ---------------------------------------------------------------------------
-def _remote_pos(owner: int, rank: int) -> int:
-    return owner if owner < rank else owner - 1
-
-
-def _split_mask(local_mask, rank, S_shard):
-    """(mask of the own shard's columns, mask of all other columns in rank order)."""
+def _split_mask(local_mask, rank, S_shard, owners):
+    """(mask of the own shard's columns, mask of the columns of the shards owned by ``owners``,
+    concatenated in that order)."""
     if local_mask is None:
         return None, None
     lo, hi = rank * S_shard, (rank + 1) * S_shard
     own = local_mask[:, :, lo:hi].contiguous()
-    rest = torch.cat([local_mask[:, :, :lo], local_mask[:, :, hi:]], dim=2).contiguous()
+    rest = None
+    if owners:
+        rest = torch.cat([local_mask[:, :, o * S_shard:(o + 1) * S_shard] for o in owners], dim=2).contiguous()
     return own, rest
 
 
 class RemoteKV:
-    """K/V of all other ranks' shards, concatenated along the sequence in rank
-    order.  For batch 1 the receive buffers ARE slices of the concatenation;
-    larger batches receive per owner and are copied into place."""
+    """K/V of the shards this rank pulls, concatenated along the sequence in rank order of their
+    owners.  Only pulled shards have a place in it, so every byte of the buffer is written by a
+    transfer before a kernel reads it.  For batch 1 the receive buffers ARE slices of the
+    concatenation; larger batches receive per owner and are copied into place."""
 
-    def __init__(self, k, v, world, rank):
+    def __init__(self, k, v, owners: List[int]):
         B, S, H, d = k.shape
-        self.B, self.S, self.world, self.rank = B, S, world, rank
-        self.k = torch.empty((B, (world - 1) * S, H, d), dtype=k.dtype, device=k.device)
-        self.v = torch.empty((B, (world - 1) * S, v.shape[2], v.shape[3]), dtype=v.dtype, device=v.device)
+        self.B, self.S, self.owners = B, S, list(owners)
+        self.pos = {o: i for i, o in enumerate(self.owners)}
+        n = len(self.owners)
+        self.k = torch.empty((B, n * S, H, d), dtype=k.dtype, device=k.device)
+        self.v = torch.empty((B, n * S, v.shape[2], v.shape[3]), dtype=v.dtype, device=v.device)
         self.tmp = {}
 
     def recv_buffers(self, owner):
-        pos = _remote_pos(owner, self.rank)
+        pos = self.pos[owner]
         ks, vs = self.k[:, pos * self.S:(pos + 1) * self.S], self.v[:, pos * self.S:(pos + 1) * self.S]
         if self.B == 1:
             return [ks, vs]
@@ -199,26 +246,107 @@ class RemoteKV:
         self.tmp = {}
 
     def slice_of(self, t, owner):
-        pos = _remote_pos(owner, self.rank)
+        pos = self.pos[owner]
         return t[:, pos * self.S:(pos + 1) * self.S]
 
 
-def cp_forward(q, k, v, remote: Optional[RemoteKV], masks, softmax_scale, sink, plan: CPPlan, ready=None):
+# ---------------------------------------------------------------------------
+# what depends on the mask only: built once per mask, reused by every forward and backward
+# ---------------------------------------------------------------------------
+@dataclass
+class CPMaskState:
+    plan: CPPlan
+    owners: List[int]                         # pulled owners in rank order
+    own_mask: Optional[torch.Tensor]
+    rest_mask: Optional[torch.Tensor]
+    own_info: Optional[FlashMaskInfo] = None  # per-K-tile reductions + launch tables of the two calls
+    rest_info: Optional[FlashMaskInfo] = None
+
+
+def _build_state(local_mask, Sq, S_shard, d, dv, plan: CPPlan) -> CPMaskState:
+    owners = plan.pull_order()
+    own, rest = _split_mask(local_mask, plan.rank, S_shard, owners)
+    st = CPMaskState(plan, owners, own, rest)
+    if local_mask is not None and local_mask.is_cuda:
+        tm, tn = bwd_tile_shape(d, dv)
+        if plan.need[plan.rank][plan.rank]:
+            st.own_info = prepare_mask(own, Sq, False, tm, tn)
+        if rest is not None:
+            st.rest_info = prepare_mask(rest, Sq, False, tm, tn)
+    return st
+
+
+# id(mask) -> (weak reference to the mask, its version counter, geometry key, state)
+_STATE_CACHE: Dict[int, tuple] = {}
+
+
+def invalidate_mask_state(local_mask=None) -> None:
+    """Forget the cached plan of ``local_mask`` (of every mask when None).  Needed only after a
+    mask tensor has been rewritten in place behind torch's back (through a raw pointer): tensor
+    identity and torch's version counter, which the cache is keyed on, do not see such a write."""
+    if local_mask is None:
+        _STATE_CACHE.clear()
+    else:
+        _STATE_CACHE.pop(id(local_mask), None)
+
+
+def mask_state(local_mask, Sq, S_shard, d, dv, ex, need_row_fn: Optional[Callable] = None) -> CPMaskState:
+    """Plan, split masks and their tile reductions for ``local_mask`` on this rank.
+
+    The need matrix costs one small all-gather and a device->host read, the split two copies of
+    the mask and the reductions two kernel launches; all of it depends on the mask only.  The
+    state is kept on the mask TENSOR: the cache entry is found by the tensor's identity, is valid
+    only while that very tensor object is alive (weak reference) and unchanged (torch version
+    counter), and never by its storage address, which the caching allocator hands out again for the
+    next step's mask.  A new mask tensor therefore always rebuilds the plan, on every rank alike."""
+    geom = (Sq, S_shard, d, dv, ex.world, ex.rank, id(ex.group))
+    if local_mask is not None:
+        ent = _STATE_CACHE.get(id(local_mask))
+        if ent is not None and ent[0]() is local_mask and ent[1] == local_mask._version and ent[2] == geom:
+            return ent[3]
+    row = (need_row_fn or shard_need_row)(local_mask, Sq, False, ex.world)
+    plan = CPPlan(ex.world, ex.rank, ex.all_gather_need(row))
+    st = _build_state(local_mask, Sq, S_shard, d, dv, plan)
+    if local_mask is not None:
+        key = id(local_mask)
+        ref = weakref.ref(local_mask, lambda _r, key=key: _STATE_CACHE.pop(key, None))
+        _STATE_CACHE[key] = (ref, local_mask._version, geom, st)
+    return st
+
+
+_EXCHANGES: Dict[int, "TorchDistExchange"] = {}
+
+
+def _exchange_for(group) -> "TorchDistExchange":
+    """One exchange object (and one side stream) per process group."""
+    ex = _EXCHANGES.get(id(group))
+    if ex is None or ex.group is not group:
+        ex = TorchDistExchange(group)
+        _EXCHANGES[id(group)] = ex
+    return ex
+
+
+def cp_forward(q, k, v, remote: Optional[RemoteKV], st: CPMaskState, softmax_scale, sink, ready=None):
     """Returns (out, lse).  ``ready``: CUDA event after which ``remote`` is complete."""
-    own_mask, rest_mask = masks
+    plan = st.plan
     need_own = plan.need[plan.rank][plan.rank]
-    need_remote = remote is not None and len(plan.pulls()) > 0
+    need_remote = remote is not None and len(st.owners) > 0
     parts = []
+    _mark("fwd:begin")
     if need_own:
-        parts.append(_flash_attn_fwd(q, k, v, own_mask, softmax_scale=softmax_scale, causal=False,
-                                     learnable_sink=sink))
+        parts.append(_flash_attn_fwd(q, k, v, st.own_mask, softmax_scale=softmax_scale, causal=False,
+                                     learnable_sink=sink, mask_info=st.own_info))
+        _mark("fwd_own")
     if need_remote:
         if ready is not None:
             torch.cuda.current_stream().wait_event(ready)
         remote.finalize()
+        _mark("fwd_wait_kv")
         # the sink logit joins the softmax once: with the first partial only
-        parts.append(_flash_attn_fwd(q, remote.k, remote.v, rest_mask, softmax_scale=softmax_scale, causal=False,
-                                     learnable_sink=None if need_own else sink))
+        parts.append(_flash_attn_fwd(q, remote.k, remote.v, st.rest_mask, softmax_scale=softmax_scale,
+                                     causal=False, learnable_sink=None if need_own else sink,
+                                     mask_info=st.rest_info))
+        _mark("fwd_remote")
     if len(parts) == 1:
         return parts[0]
     B, Sq, Hq, _ = q.shape
@@ -230,19 +358,21 @@ def cp_forward(q, k, v, remote: Optional[RemoteKV], masks, softmax_scale, sink, 
     lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device)
     _merge(acc, lse, parts[0][0], parts[0][1], True)
     _merge(acc, lse, parts[1][0], parts[1][1], False)
-    return _cast(acc, q), lse
+    out = _cast(acc, q)
+    _mark("fwd_merge")
+    return out, lse
 
 
-def cp_backward_remote(q, remote, out, dout, lse, rest_mask, softmax_scale, deterministic):
+def cp_backward_remote(q, remote, out, dout, lse, st: CPMaskState, softmax_scale, deterministic):
     """Gradients of the remote call: (dq_remote, dk_all_remote, dv_all_remote)."""
-    dq, dk, dv, _ = _flash_attn_bwd(q, remote.k, remote.v, out, dout, lse, rest_mask, softmax_scale=softmax_scale,
-                                    causal=False, deterministic=deterministic)
+    dq, dk, dv, _ = _flash_attn_bwd(q, remote.k, remote.v, out, dout, lse, st.rest_mask, softmax_scale=softmax_scale,
+                                    causal=False, deterministic=deterministic, mask_info=st.rest_info)
     return dq, dk, dv
 
 
-def cp_backward_own(q, k, v, out, dout, lse, own_mask, softmax_scale, sink, deterministic):
-    return _flash_attn_bwd(q, k, v, out, dout, lse, own_mask, softmax_scale=softmax_scale, causal=False,
-                           learnable_sink=sink, deterministic=deterministic)
+def cp_backward_own(q, k, v, out, dout, lse, st: CPMaskState, softmax_scale, sink, deterministic):
+    return _flash_attn_bwd(q, k, v, out, dout, lse, st.own_mask, softmax_scale=softmax_scale, causal=False,
+                           learnable_sink=sink, deterministic=deterministic, mask_info=st.own_info)
 
 
 def _sum_dq(dq_a, dq_b):
@@ -268,77 +398,61 @@ def _dsink_only(q, k, v, out, dout, lse, sink, softmax_scale):
 # ---------------------------------------------------------------------------
 # autograd entry for real process groups
 # ---------------------------------------------------------------------------
-_PLAN_CACHE: Dict[tuple, CPPlan] = {}
-
-
-def build_plan(local_mask, Sq, causal, ex: TorchDistExchange) -> CPPlan:
-    """The need matrix costs one small all-gather and a device->host read; it
-    depends on the mask only, so it is kept per (mask storage, version, group)."""
-    key = None
-    if local_mask is not None:
-        key = (local_mask.data_ptr(), local_mask._version, tuple(local_mask.shape), Sq, ex.world, ex.rank,
-               id(ex.group))
-        if key in _PLAN_CACHE:
-            return _PLAN_CACHE[key]
-    row = shard_need_row(local_mask, Sq, causal, ex.world)
-    plan = CPPlan(ex.world, ex.rank, ex.all_gather_need(row))
-    if key is not None:
-        if len(_PLAN_CACHE) > 64:
-            _PLAN_CACHE.clear()
-        _PLAN_CACHE[key] = plan
-    return plan
-
-
 class _CPFunc(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, local_mask, softmax_scale, sink, deterministic, group):
-        ex = TorchDistExchange(group)
-        plan = build_plan(local_mask, q.shape[1], False, ex)
+        ex = _exchange_for(group)
         k, v = k.contiguous(), v.contiguous()
-        remote = RemoteKV(k, v, plan.world, plan.rank)
+        st = mask_state(local_mask, q.shape[1], k.shape[1], q.shape[3], v.shape[3], ex)
+        plan = st.plan
+        remote = RemoteKV(k, v, st.owners)
         recv = {o: remote.recv_buffers(o) for o in plan.pulls()}
         send = {t: [k, v] for t in plan.pushes()}
         ready = ex.exchange(send, recv)                     # overlaps with the own-shard call below
-        masks = _split_mask(local_mask, plan.rank, k.shape[1])
-        out, lse = cp_forward(q, k, v, remote, masks, softmax_scale, sink, plan, ready)
+        out, lse = cp_forward(q, k, v, remote, st, softmax_scale, sink, ready)
         torch.cuda.current_stream().wait_stream(ex.comm_stream)
-        ctx.save_for_backward(q, k, v, local_mask, out, lse, sink)
-        ctx.remote, ctx.plan, ctx.ex = remote, plan, ex      # pulled shards are kept for the backward
+        ctx.save_for_backward(q, k, v, out, lse, sink)
+        ctx.remote, ctx.st, ctx.ex = remote, st, ex          # pulled shards are kept for the backward
         ctx.softmax_scale, ctx.deterministic = softmax_scale, deterministic
         ctx.mark_non_differentiable(lse)
         return out, lse
 
     @staticmethod
     def backward(ctx, dout, dlse):
-        q, k, v, local_mask, out, lse, sink = ctx.saved_tensors
-        plan, ex, remote = ctx.plan, ctx.ex, ctx.remote
+        q, k, v, out, lse, sink = ctx.saved_tensors
+        st, ex, remote = ctx.st, ctx.ex, ctx.remote
+        plan = st.plan
         det = ctx.deterministic
         if det is None:
             det = torch.are_deterministic_algorithms_enabled()
         dout = dout.contiguous()
-        own_mask, rest_mask = _split_mask(local_mask, plan.rank, k.shape[1])
         need_own = plan.need[plan.rank][plan.rank]
         dq_r = None
         send, ready = {}, None
         recv = {t: [torch.empty_like(k), torch.empty_like(v)] for t in plan.pushes()}
-        if plan.pulls():
-            dq_r, dk_all, dv_all = cp_backward_remote(q, remote, out, dout, lse, rest_mask, ctx.softmax_scale, det)
+        _mark("bwd:begin")
+        if st.owners:
+            dq_r, dk_all, dv_all = cp_backward_remote(q, remote, out, dout, lse, st, ctx.softmax_scale, det)
             send = {o: [remote.slice_of(dk_all, o).contiguous(), remote.slice_of(dv_all, o).contiguous()]
                     for o in plan.pulls()}
+            _mark("bwd_remote")
         if send or recv:
             ready = ex.exchange_reverse(send, recv)          # overlaps with the own-shard call below
         dq_o = dsink = None
         own = None
         if need_own:
-            dq_o, dk_o, dv_o, dsink = cp_backward_own(q, k, v, out, dout, lse, own_mask, ctx.softmax_scale, sink, det)
+            dq_o, dk_o, dv_o, dsink = cp_backward_own(q, k, v, out, dout, lse, st, ctx.softmax_scale, sink, det)
             own = (dk_o, dv_o)
+            _mark("bwd_own")
         elif sink is not None:
             dsink = _dsink_only(q, k, v, out, dout, lse, sink, ctx.softmax_scale)
         dq = _sum_dq(dq_o, dq_r)
         if dq is None:
             dq = torch.zeros_like(q)
+        _mark("bwd_dq_sum")
         if ready is not None:
             torch.cuda.current_stream().wait_event(ready)
+        _mark("bwd_wait_dkv")
         by_rank = {t: ts for t, ts in recv.items()}
         if own is not None:
             by_rank[plan.rank] = list(own)
@@ -348,6 +462,7 @@ class _CPFunc(torch.autograd.Function):
             dv = _reduce_partials([by_rank[r][1] for r in ranks])
         else:
             dk, dv = torch.zeros_like(k), torch.zeros_like(v)
+        _mark("bwd_reduce_dkv")
         torch.cuda.current_stream().wait_stream(ex.comm_stream)
         return dq, dk, dv, None, None, dsink, None, None
 
@@ -395,11 +510,13 @@ def cp_flashmask_attention(query, key, value, startend_row_indices=None, *, caus
 # ---------------------------------------------------------------------------
 # single-process emulation (all ranks on one GPU)
 # ---------------------------------------------------------------------------
-def emulate_cp(qs, ks, vs, douts, local_masks, softmax_scale=None, sink=None, deterministic=True):
+def emulate_cp(qs, ks, vs, douts, local_masks, softmax_scale=None, sink=None, deterministic=True, poison=None):
     """Run the context-parallel schedule for ``world = len(qs)`` ranks inside
     one process (tests of the arithmetic and of the schedule without several
     GPUs): plans, forward, backward partials, owner reductions, with exchanges
-    replaced by copies.  Returns per-rank lists (out, lse, dq, dk, dv) and dsink."""
+    replaced by copies.  ``poison``: value the receive buffers are filled with before the copies
+    (a test passes NaN to show that nothing a kernel reads is left unwritten).  Returns per-rank
+    lists (out, lse, dq, dk, dv) and dsink."""
     world = len(qs)
     Sq = qs[0].shape[1]
     S = ks[0].shape[1]
@@ -410,27 +527,29 @@ def emulate_cp(qs, ks, vs, douts, local_masks, softmax_scale=None, sink=None, de
     plans = [CPPlan(world, r, need) for r in range(world)]
     ks = [k.contiguous() for k in ks]
     vs = [v.contiguous() for v in vs]
+    d, dvd = qs[0].shape[3], vs[0].shape[3]
+    states = [_build_state(local_masks[r], Sq, S, d, dvd, plans[r]) for r in range(world)]
     remotes, outs, lses = [], [], []
     for r in range(world):
-        rem = RemoteKV(ks[r], vs[r], world, r)
+        rem = RemoteKV(ks[r], vs[r], states[r].owners)
+        if poison is not None:
+            rem.k.fill_(poison); rem.v.fill_(poison)
         for o in plans[r].pulls():
             bufs = rem.recv_buffers(o)
             bufs[0].copy_(ks[o]); bufs[1].copy_(vs[o])
         remotes.append(rem)
-        out, lse = cp_forward(qs[r], ks[r], vs[r], rem, _split_mask(local_masks[r], r, S), softmax_scale, sink,
-                              plans[r])
+        out, lse = cp_forward(qs[r], ks[r], vs[r], rem, states[r], softmax_scale, sink)
         outs.append(out); lses.append(lse)
     dqs, contrib, dsinks = [], {o: {} for o in range(world)}, []
     for r in range(world):
-        own_mask, rest_mask = _split_mask(local_masks[r], r, S)
         dq_r = dq_o = ds = None
-        if plans[r].pulls():
-            dq_r, dk_all, dv_all = cp_backward_remote(qs[r], remotes[r], outs[r], douts[r], lses[r], rest_mask,
+        if states[r].owners:
+            dq_r, dk_all, dv_all = cp_backward_remote(qs[r], remotes[r], outs[r], douts[r], lses[r], states[r],
                                                       softmax_scale, deterministic)
             for o in plans[r].pulls():
                 contrib[o][r] = (remotes[r].slice_of(dk_all, o), remotes[r].slice_of(dv_all, o))
         if need[r][r]:
-            dq_o, dk_o, dv_o, ds = cp_backward_own(qs[r], ks[r], vs[r], outs[r], douts[r], lses[r], own_mask,
+            dq_o, dk_o, dv_o, ds = cp_backward_own(qs[r], ks[r], vs[r], outs[r], douts[r], lses[r], states[r],
                                                    softmax_scale, sink, deterministic)
             contrib[r][r] = (dk_o, dv_o)
         elif sink is not None:

@@ -1,5 +1,6 @@
 // extern "C" entry points: argument validation, kernel-variant selection,
 // workspace carving.  No allocation, no host synchronisation.
+#include <atomic>
 #include <cstdarg>
 #include <cstdlib>
 #include <cstring>
@@ -16,6 +17,9 @@ void set_error(const char* fmt, ...) {
   vsnprintf(g_err, sizeof(g_err), fmt, ap);
   va_end(ap);
 }
+
+static std::atomic<unsigned long long> g_launches{0};
+void count_launches(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 
 int cuda_fail(cudaError_t e, const char* what) {
   set_error("CUDA error %d (%s) at %s", (int)e, cudaGetErrorString(e), what);
@@ -34,9 +38,6 @@ int fwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s
 bool bwd_sm100_supported(const fm_attn_args* a);
 int bwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s);
 int bwd_sm100_persist_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s);
-bool fwd_sm100_persist_supported(const fm_attn_args* a);
-int fwd_sm100_persist_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s);
-int fwd_sm100_persist_status(int* out, bool reset);
 int bwd_sm100_persist_status(int* out, bool reset);
 size_t bwd_sm100_workspace_bytes(const fm_attn_args* a);
 
@@ -46,12 +47,29 @@ int bounded_wait_selftest_launch(uint64_t budget_ns, cudaStream_t s);
 
 static inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
+// A/B switches, read from the environment ONCE when the library is loaded (and again only when
+// the host asks through fm_reload_options): no entry point touches the environment per call.
+//   FLASHMASK_B200_FWD=mma       forward on the warp-MMA kernels for every head dim
+//   FLASHMASK_B200_BWD=mma       backward on the warp-MMA kernels for every head dim
+//   FLASHMASK_B200_PERSIST=0     tcgen05 backward: one unit per CTA even with launch tables
+//   FLASHMASK_B200_CLASSES=n     work classes of the launch tables (1..8)
+struct Options { bool fwd_mma, bwd_mma, bwd_persist; int order_classes; };
+static Options read_options() {
+  Options o{false, false, true, 0};
+  if (const char* e = getenv("FLASHMASK_B200_FWD")) o.fwd_mma = strcmp(e, "mma") == 0;
+  if (const char* e = getenv("FLASHMASK_B200_BWD")) o.bwd_mma = strcmp(e, "mma") == 0;
+  if (const char* e = getenv("FLASHMASK_B200_PERSIST")) o.bwd_persist = !(e[0] == '0' && e[1] == 0);
+  if (const char* e = getenv("FLASHMASK_B200_CLASSES")) o.order_classes = atoi(e);
+  return o;
+}
+static Options g_opt = read_options();
+int option_order_classes() { return g_opt.order_classes; }
+
 // Kernel variant of the forward for (d, dv): the tcgen05 kernels cover head dims up to
 // 128 (multiples of 8); FLASHMASK_B200_FWD=mma forces the warp-MMA variant (A/B runs).
 static bool fwd_uses_sm100(int d, int dv) {
   if (d > 128 || dv > 128 || d % 8 || dv % 8) return false;
-  const char* e = getenv("FLASHMASK_B200_FWD");
-  return !(e && strcmp(e, "mma") == 0);
+  return !g_opt.fwd_mma;
 }
 
 static bool stride_ok(const int64_t* s) { return s[0] % 8 == 0 && s[1] % 8 == 0 && s[2] % 8 == 0; }
@@ -123,10 +141,16 @@ using namespace fm;
 extern "C" const char* fm_version(void) { return "flashmask_b200 0.1.0 sm_100a"; }
 extern "C" const char* fm_last_error(void) { return g_err; }
 
+extern "C" unsigned long long fm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+extern "C" int fm_reload_options(void) {
+  g_opt = read_options();
+  return FM_OK;
+}
+
 static bool bwd_uses_sm100(int d, int dv) {
   if (d > 128 || dv > 128 || d % 8 || dv % 8) return false;
-  const char* e = getenv("FLASHMASK_B200_BWD");
-  return !(e && strcmp(e, "mma") == 0);
+  return !g_opt.bwd_mma;
 }
 
 // preprocess -> main kernels of the selected variant -> dsink, on one stream
@@ -140,8 +164,7 @@ static int run_bwd_kernels(const fm_attn_args* a, const AttnKParams& p, cudaStre
     // (documents, windows) and 3-5 % slower where every unit is hundreds of items long (its main loop
     // is slightly slower; the table records in [E+2] which side of that line a mask is on).
     // FLASHMASK_B200_PERSIST=0 keeps the one-unit-per-CTA variant.
-    const char* pe = getenv("FLASHMASK_B200_PERSIST");
-    const bool persist = p.dq_order && p.dkdv_order && !(pe && pe[0] == '0' && pe[1] == 0);
+    const bool persist = p.dq_order && p.dkdv_order && g_opt.bwd_persist;
     rc = persist ? bwd_sm100_persist_launch(p, a, s) : bwd_sm100_launch(p, a, s);
   } else {
     rc = bwd_mma_launch(p, a->dtype, s);
@@ -150,8 +173,6 @@ static int run_bwd_kernels(const fm_attn_args* a, const AttnKParams& p, cudaStre
   if (a->sink) rc = bwd_dsink_launch(p, s);
   return rc;
 }
-
-static bool attach_fwd_table(const fm_attn_args* a, AttnKParams* p);
 
 extern "C" int fm_fwd_tile_shape(int d, int dv, int* tile_m, int* tile_n) {
   FM_REQUIRE(tile_m && tile_n, FM_ERR_INVALID_ARGUMENT, "fm_fwd_tile_shape: NULL output");
@@ -198,15 +219,7 @@ static int fwd_impl(const fm_attn_args* a, const BlockScore& bs, void* stream) {
     FM_REQUIRE(!fwd_uses_sm100(a->d, a->dv), FM_ERR_INVALID_ARGUMENT, "fm_fwd_block_score: q/k/v must be 16-byte aligned");
     return fwd_mma_launch(p, a->dtype, (cudaStream_t)stream);
   }
-  if (fwd_uses_sm100(a->d, a->dv) && fwd_sm100_supported(a)) {
-    // with a launch table (a mask tensor) the persistent variant can walk it (FLASHMASK_B200_FWD_PERSIST=1);
-    // the one-unit-per-CTA kernel reads its table entry at CTA start
-    const char* pe = getenv("FLASHMASK_B200_FWD_PERSIST");
-    if (p.fwd_order && pe && pe[0] == '1' && pe[1] == 0 && fwd_sm100_persist_supported(a) &&
-        attach_fwd_table(a, &p))
-      return fwd_sm100_persist_launch(p, a, (cudaStream_t)stream);
-    return fwd_sm100_launch(p, a, (cudaStream_t)stream);
-  }
+  if (fwd_uses_sm100(a->d, a->dv) && fwd_sm100_supported(a)) return fwd_sm100_launch(p, a, (cudaStream_t)stream);
   FM_REQUIRE(!fwd_uses_sm100(a->d, a->dv), FM_ERR_INVALID_ARGUMENT,
              "fm_fwd: q/k/v must be 16-byte aligned");
   return fwd_mma_launch(p, a->dtype, (cudaStream_t)stream);
@@ -263,16 +276,6 @@ extern "C" int64_t fm_launch_order_ints(const fm_attn_args* a, int which) {
 }
 
 // The counters of the persistent kernels live behind the table and the two unit arrays.
-static bool attach_fwd_table(const fm_attn_args* a, AttnKParams* p) {
-  OrderGeom g;
-  p->fwd_sched = nullptr;
-  p->fwd_ncta = 0;
-  if (!p->fwd_order || !order_geometry_any(a, FM_ORDER_FWD, &g)) return false;
-  p->fwd_ncta = (int)g.n_cta;
-  p->fwd_sched = const_cast<int*>(p->fwd_order) + 2 * g.n_cta + 2 * g.E;
-  return true;
-}
-
 static void attach_bwd_tables(const fm_attn_args* a, AttnKParams* p) {
   OrderGeom g;
   p->dq_sched = p->dkdv_sched = nullptr;
@@ -369,11 +372,9 @@ extern "C" int fm_kernel_status(int* status, int reset) {
   if (rc != FM_OK) return rc;
   rc = bwd_sm100_status(&bw, reset != 0);
   if (rc != FM_OK) return rc;
-  int bp = 0, fp = 0;
+  int bp = 0;
   rc = bwd_sm100_persist_status(&bp, reset != 0);
-  if (rc != FM_OK) return rc;
-  rc = fwd_sm100_persist_status(&fp, reset != 0);
-  *status = f ? f : (bw ? bw : (bp ? bp : fp));
+  *status = f ? f : (bw ? bw : bp);
   return rc;
 }
 

@@ -21,8 +21,8 @@ struct AttnKParams {
   const int32_t* fwd_order; const int32_t* dq_order; const int32_t* dkdv_order;
   // state behind a backward table: [0] next table entry, [1] CTAs that left, [2] 1 when the persistent
   // variant runs on this table, 0 when the one-unit-per-CTA variant does (written by the table builder)
-  int* dq_sched; int* dkdv_sched; int* fwd_sched;
-  int dq_ncta, dkdv_ncta, fwd_ncta;   // entries of the tables
+  int* dq_sched; int* dkdv_sched;
+  int dq_ncta, dkdv_ncta;   // entries of the tables
   // optional side output of the forward: per (query row, block of key columns) the maximum of the
   // masked, scaled scores, combined into block_logit[b][head][row][block] with fmax; block ids are
   // relative to block_bos[b][row] (the first key of the row's document) when that is given
@@ -49,5 +49,7 @@ struct OrderJob { int axis, block_rows, n_units, n_other, rep_h, rep_b, heads, i
 struct OrderJobs { OrderJob job[3]; };
 // Builds up to three tables in one launch (one CTA each).
 int launch_order_build(const MaskDesc& md, int tile_n, const OrderJobs& jobs, int n_jobs, cudaStream_t s);
+// Work classes requested through the environment when the library was loaded (0: the default).
+int option_order_classes();
 
 }  // namespace fm

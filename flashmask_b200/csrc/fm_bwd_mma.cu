@@ -461,6 +461,7 @@ static int launch_bwd(const AttnKParams& p, int dtype, cudaStream_t s) {
     FM_CUDA_TRY(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
     k1<<<dim3(nb, p.Hkv, p.B), 256, Cfg::SMEM, s>>>(p);
     k2<<<dim3(tq, p.Hq, p.B), 256, Cfg::SMEM, s>>>(p);
+    count_launches(2);
   } else {
     auto k1 = bwd_dkdv_mma_kernel<D, DV, BR, BC, false>;
     auto k2 = bwd_dq_mma_kernel<D, DV, BR, BC, false>;
@@ -468,6 +469,7 @@ static int launch_bwd(const AttnKParams& p, int dtype, cudaStream_t s) {
     FM_CUDA_TRY(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
     k1<<<dim3(nb, p.Hkv, p.B), 256, Cfg::SMEM, s>>>(p);
     k2<<<dim3(tq, p.Hq, p.B), 256, Cfg::SMEM, s>>>(p);
+    count_launches(2);
   }
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
@@ -487,6 +489,7 @@ static void launch_preprocess(const AttnKParams& p, int dtype, cudaStream_t s) {
   dim3 grid((p.Sq_r + rows_per_block - 1) / rows_per_block, p.Hq, p.B);
   if (dtype == FM_DTYPE_BF16) bwd_preprocess_kernel<true, LPR><<<grid, 256, 0, s>>>(p);
   else bwd_preprocess_kernel<false, LPR><<<grid, 256, 0, s>>>(p);
+  count_launches(1);
 }
 
 int bwd_preprocess_launch(const AttnKParams& p, int dtype, cudaStream_t s) {
@@ -500,6 +503,7 @@ int bwd_preprocess_launch(const AttnKParams& p, int dtype, cudaStream_t s) {
 
 int bwd_dsink_launch(const AttnKParams& p, cudaStream_t s) {
   bwd_dsink_kernel<<<p.Hq, 256, 0, s>>>(p);
+  count_launches(1);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }

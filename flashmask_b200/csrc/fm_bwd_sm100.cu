@@ -553,6 +553,7 @@ static int launch_bwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStr
   k1<<<dim3((p.Sk + 127) / 128, p.Hkv, p.B), Cfg::NTHREADS, Cfg::SMEM, s>>>(k128, v128, q64, do64, p);
   FM_CUDA_TRY(cudaGetLastError());
   k2<<<dim3((p.Sq + 127) / 128, p.Hq, p.B), Cfg::NTHREADS, Cfg::SMEM, s>>>(q128, do128, k64, v64, p);
+  count_launches(2);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }

@@ -701,6 +701,7 @@ static int launch_bwd_sm100_persist(const AttnKParams& p, const fm_attn_args* a,
   k1<<<g1, Cfg::NTHREADS, Cfg::SMEM, s>>>(k128, v128, q64, do64, p);
   FM_CUDA_TRY(cudaGetLastError());
   k2<<<g2, Cfg::NTHREADS, Cfg::SMEM, s>>>(q128, do128, k64, v64, p);
+  count_launches(2);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }

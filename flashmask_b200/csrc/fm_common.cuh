@@ -17,6 +17,8 @@ namespace fm {
 // error plumbing (host)
 // ---------------------------------------------------------------------------
 void set_error(const char* fmt, ...);
+// Every host function that launches kernels reports how many (fm_launch_count sums them).
+void count_launches(int n);
 int cuda_fail(cudaError_t e, const char* what);
 
 #define FM_CUDA_TRY(expr)                                     \

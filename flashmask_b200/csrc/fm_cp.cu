@@ -198,6 +198,7 @@ extern "C" int fm_cp_chunk_workload(const int32_t* valid_cnt, int B, int Hm, int
   const int n_chunks = (Tq + blocks_per_chunk - 1) / blocks_per_chunk;
   cp_chunk_workload_kernel<<<dim3((n_chunks + 127) / 128, Hm), 128, 0, (cudaStream_t)stream>>>(
       valid_cnt, B, Hm, Tq, blocks_per_chunk, n_chunks, out);
+  count_launches(1);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }
@@ -209,6 +210,7 @@ extern "C" int fm_cp_rerank(const int32_t* mask, const int32_t* chunk_idx, int32
   const int64_t total = (int64_t)B * H * n_chunks * chunk_size * D;
   cp_rerank_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(mask, chunk_idx, out, B * H, S,
                                                                                       D, n_chunks, chunk_size);
+  count_launches(1);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }
@@ -219,6 +221,7 @@ extern "C" int fm_cp_localize(const int32_t* mask, const int32_t* local_chunk_id
              "fm_cp_localize: bad arguments");
   cp_localize_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(mask, local_chunk_idx, out, n,
                                                                                     n_local, chunk_size);
+  count_launches(1);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }
@@ -229,6 +232,7 @@ extern "C" int fm_cp_shard_visible(const int32_t* mask, int B, int Hm, int Sq, i
              FM_ERR_INVALID_ARGUMENT, "fm_cp_shard_visible: Sk must be a multiple of the shard count");
   MaskDesc md{mask, nullptr, ncols, causal, Hm, B, 0, B * Hm, Sq, Sk};
   cp_shard_visible_kernel<<<dim3(n_shards, B * Hm), 256, 0, (cudaStream_t)stream>>>(md, Sk / n_shards, n_shards, out);
+  count_launches(1);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }
@@ -242,6 +246,7 @@ extern "C" int fm_cp_merge_partial(float* acc, float* lse_run, const void* o_s, 
     cp_merge_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(acc, lse_run, (const uint16_t*)o_s, lse_s, B, S, H, dv, first);
   else
     cp_merge_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(acc, lse_run, (const uint16_t*)o_s, lse_s, B, S, H, dv, first);
+  count_launches(1);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }
@@ -251,6 +256,7 @@ extern "C" int fm_cp_accumulate(float* acc, const void* x, int64_t n, int dtype,
   const unsigned grid = (unsigned)((n / 4 + 255) / 256);
   if (dtype == FM_DTYPE_BF16) cp_add_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(acc, (const uint16_t*)x, n, first);
   else cp_add_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(acc, (const uint16_t*)x, n, first);
+  count_launches(1);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }
@@ -260,6 +266,7 @@ extern "C" int fm_cp_cast(const float* acc, void* out, int64_t n, int dtype, voi
   const unsigned grid = (unsigned)((n / 4 + 255) / 256);
   if (dtype == FM_DTYPE_BF16) cp_cast_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(acc, (uint16_t*)out, n);
   else cp_cast_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(acc, (uint16_t*)out, n);
+  count_launches(1);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }
@@ -278,6 +285,7 @@ extern "C" int fm_cp_reduce_partials(const void* const* parts, int n_parts, void
     cp_reduce_partials_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(pp, n_parts, (uint16_t*)out, n);
   else
     cp_reduce_partials_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(pp, n_parts, (uint16_t*)out, n);
+  count_launches(1);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }

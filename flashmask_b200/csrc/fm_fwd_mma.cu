@@ -275,10 +275,12 @@ static int launch_fwd(const AttnKParams& p, int dtype, cudaStream_t s) {
     auto kern = fwd_mma_kernel<D, DV, BR, BC, NSPLIT, true>;
     FM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CfgB::SMEM));
     kern<<<grid, CfgB::NTHREADS, CfgB::SMEM, s>>>(p);
+    count_launches(1);
   } else {
     auto kern = fwd_mma_kernel<D, DV, BR, BC, NSPLIT, false>;
     FM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CfgB::SMEM));
     kern<<<grid, CfgB::NTHREADS, CfgB::SMEM, s>>>(p);
+    count_launches(1);
   }
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;

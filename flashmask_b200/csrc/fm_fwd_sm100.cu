@@ -527,6 +527,7 @@ __global__ void bounded_wait_selftest_kernel(uint64_t budget_ns) {
 
 int bounded_wait_selftest_launch(uint64_t budget_ns, cudaStream_t s) {
   bounded_wait_selftest_kernel<<<1, 64, 0, s>>>(budget_ns);
+  count_launches(1);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }
@@ -552,6 +553,7 @@ static int launch_fwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStr
   FM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   dim3 grid((p.Sq + 255) / 256, p.Hq, p.B);
   kern<<<grid, Cfg::NTHREADS, smem_bytes, s>>>(tq, tk, tv, p);
+  count_launches(1);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }

@@ -229,7 +229,7 @@ int fm::launch_order_build(const MaskDesc& md, int tile_n, const OrderJobs& jobs
     smem = std::max(smem, sizeof(int32_t) * (2 * E + FM_ORDER_BUCKETS + 1 + 32) + E);
   }
   int n_classes = FM_ORDER_BUCKETS;
-  if (const char* e = getenv("FLASHMASK_B200_CLASSES")) n_classes = std::min(FM_ORDER_BUCKETS, std::max(1, atoi(e)));
+  if (const int e = option_order_classes()) n_classes = std::min(FM_ORDER_BUCKETS, std::max(1, e));
   // staging area for the reductions: 8 x BHm x nblk_pad ints, only when that stays small
   const size_t stage_ints = 8 * (size_t)md.BHm * md.nblk_pad;
   const int staged = (stage_ints * 4 + smem <= 96 * 1024 && (reinterpret_cast<uintptr_t>(md.minmax) & 15) == 0)
@@ -238,6 +238,7 @@ int fm::launch_order_build(const MaskDesc& md, int tile_n, const OrderJobs& jobs
   if (smem > 48 * 1024)
     FM_CUDA_TRY(cudaFuncSetAttribute(launch_order_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
   launch_order_kernel<<<n_jobs, 1024, smem, s>>>(md, tile_n, jobs, n_classes, staged, staged);
+  count_launches(1);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }
@@ -270,6 +271,7 @@ extern "C" int fm_mask_prepare(const int32_t* mask, int B, int Hm, int Sq, int S
     if (ncols == 1) scan_minmax_kernel<1><<<grid, 128, 0, s>>>(mask, minmax, BHm, Sk, tile_n, nb, pad, causal);
     else if (ncols == 2) scan_minmax_kernel<2><<<grid, 128, 0, s>>>(mask, minmax, BHm, Sk, tile_n, nb, pad, causal);
     else scan_minmax_kernel<4><<<grid, 128, 0, s>>>(mask, minmax, BHm, Sk, tile_n, nb, pad, causal);
+    count_launches(1);
     FM_CUDA_TRY(cudaGetLastError());
   }
   if (valid_cnt || tile_class) {
@@ -277,6 +279,7 @@ extern "C" int fm_mask_prepare(const int32_t* mask, int B, int Hm, int Sq, int S
     const int tq = (Sq + tile_m - 1) / tile_m;
     dim3 grid((tq + 3) / 4, BHm);
     classify_kernel<<<grid, 128, 0, s>>>(md, tile_m, tile_n, tq, nb, valid_cnt, tile_class);
+    count_launches(1);
     FM_CUDA_TRY(cudaGetLastError());
   }
   return FM_OK;
@@ -288,6 +291,7 @@ extern "C" int fm_mask_count_visible(const int32_t* mask, int B, int Hm, int Sq,
              "fm_mask_count_visible: needs a mask with 1, 2 or 4 columns");
   MaskDesc md{mask, nullptr, ncols, causal, Hm, B, 0, B * Hm, Sq, Sk};
   count_visible_kernel<<<B * Hm, 256, 0, (cudaStream_t)stream>>>(md, out);
+  count_launches(1);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;
 }

@@ -15,7 +15,7 @@ from typing import Optional, Tuple, Union
 
 import torch
 
-from .ops import _flash_attn_bwd, _flash_attn_fwd
+from .ops import _flash_attn_bwd, _flash_attn_fwd, fwd_tile_shape, prepare_mask
 
 __all__ = ["flashmask_attention", "FlashMaskFunc", "sliding_window_indices"]
 
@@ -24,9 +24,17 @@ class FlashMaskFunc(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, startend_row_indices, softmax_scale, causal, learnable_sink,
                 deterministic):
+        # the mask is scanned once: forward and backward share its per-K-tile reductions and the
+        # launch tables whenever their kernel variants tile the keys alike
+        info = None
+        if startend_row_indices is not None:
+            tm, tn = fwd_tile_shape(q.shape[-1], v.shape[-1])
+            info = prepare_mask(startend_row_indices, q.shape[1], causal, tm, tn)
         out, lse = _flash_attn_fwd(q, k, v, startend_row_indices, softmax_scale=softmax_scale,
-                                   causal=causal, learnable_sink=learnable_sink, return_lse=True)
+                                   causal=causal, learnable_sink=learnable_sink, return_lse=True,
+                                   mask_info=info)
         ctx.save_for_backward(q, k, v, startend_row_indices, out, lse, learnable_sink)
+        ctx.mask_info = info
         ctx.softmax_scale = softmax_scale
         ctx.causal = causal
         ctx.deterministic = deterministic
@@ -40,7 +48,8 @@ class FlashMaskFunc(torch.autograd.Function):
         if det is None:
             det = torch.are_deterministic_algorithms_enabled()
         dq, dk, dv, dsink = _flash_attn_bwd(q, k, v, out, dout, lse, idx, softmax_scale=ctx.softmax_scale,
-                                            causal=ctx.causal, learnable_sink=sink, deterministic=det)
+                                            causal=ctx.causal, learnable_sink=sink, deterministic=det,
+                                            mask_info=ctx.mask_info)
         return dq, dk, dv, None, None, None, dsink, None
 
 

@@ -171,10 +171,17 @@ def _check_shapes(q, k, v, idx, causal):
             assert idx.shape[-1] in (2, 4), "non-causal masks carry 2 or 4 bounds per column"
 
 
+# head-dim pairs for which the reference folds dV into dK when value aliases key
+# (_LARGE_HDIMS, flashmask/cute/ops/bwd.py:136-139)
+_KV_SHARED_HDIMS = ((512, 512), (576, 512))
+
+
 def _kv_shared(k: torch.Tensor, v: torch.Tensor) -> bool:
-    """True when ``v`` is ``k[..., :dv]`` on the same storage (MLA-style shared K/V)."""
-    return (v.data_ptr() == k.data_ptr() and v.shape[-1] <= k.shape[-1] and v.shape[:-1] == k.shape[:-1]
-            and v.stride() == k.stride())
+    """True when ``v`` is ``k[..., :dv]`` on the same storage (MLA-style shared K/V) at one of the
+    head-dim pairs for which the reference merges the two gradients; at every other head dim an
+    aliased value keeps its own dV, as in the reference."""
+    return ((k.shape[-1], v.shape[-1]) in _KV_SHARED_HDIMS
+            and v.data_ptr() == k.data_ptr() and v.shape[:-1] == k.shape[:-1] and v.stride() == k.stride())
 
 
 def _sink_fp32(sink, Hq, device):

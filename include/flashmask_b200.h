@@ -135,10 +135,14 @@ typedef struct fm_attn_args {
   int64_t dq_stride[3];
   int64_t dk_stride[3];
   int64_t dv_stride[3];
-  /* Optional launch orders from fm_launch_order (NULL: tiles in index order). */
+  /* Optional launch orders from fm_launch_order (NULL: tiles in index order).
+   * The entries are only read, but the 4 counters at the end of a backward table
+   * are advanced and rewound by every fm_bwd launch that walks it: a table must not
+   * be shared by two backward launches that can overlap on the GPU (two streams
+   * without an ordering between them); build one table per stream instead. */
   const int32_t* fwd_order;  /* FM_ORDER_FWD, read by fm_fwd                     */
-  const int32_t* dq_order;   /* FM_ORDER_BWD_DQ, read by fm_bwd                  */
-  const int32_t* dkdv_order; /* FM_ORDER_BWD_DKDV, read by fm_bwd                */
+  const int32_t* dq_order;   /* FM_ORDER_BWD_DQ, walked by fm_bwd                */
+  const int32_t* dkdv_order; /* FM_ORDER_BWD_DKDV, walked by fm_bwd              */
 } fm_attn_args;
 
 /* Tile shape (rows of Q, columns of K per tile) the forward / backward kernel
@@ -148,6 +152,22 @@ typedef struct fm_attn_args {
  * (flashmask/cute/ops/_common.py:95-132). */
 FM_API int fm_fwd_tile_shape(int d, int dv, int* tile_m, int* tile_n);
 FM_API int fm_bwd_tile_shape(int d, int dv, int* tile_m, int* tile_n);
+
+/* The library reads its A/B switches from the environment once, when it is loaded
+ * (FLASHMASK_B200_FWD=mma / FLASHMASK_B200_BWD=mma: warp-MMA kernels for every head
+ * dim; FLASHMASK_B200_BWD=split: the two-kernel tcgen05 backward even when
+ * args->deterministic is 0; FLASHMASK_B200_PERSIST=0: one unit per CTA in that
+ * backward; FLASHMASK_B200_CLASSES=n: work classes of the launch tables).  A host
+ * that changes them afterwards calls fm_reload_options() to have them read again;
+ * no other entry point touches the environment.  No counterpart in the reference,
+ * which reads its switches per call in Python. */
+FM_API int fm_reload_options(void);
+
+/* Number of kernels this library has launched in this process so far (all
+ * entry points, all streams).  A benchmark reads it before and after its timed
+ * region to state how many launches that region made.  No counterpart in the
+ * reference. */
+FM_API unsigned long long fm_launch_count(void);
 
 /* Forward: O = softmax(QK^T*scale + M [, sink]) V and LSE.
  * Replaces _flash_attn_fwd (flashmask/cute/ops/fwd.py:52-882) +

@@ -24,3 +24,14 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _library_options_follow_the_environment():
+    """The library reads its FLASHMASK_B200_* switches once at load.  Tests that change them call
+    ``_lib.reload_options()`` after setting the variable; this fixture is torn down after
+    monkeypatch has restored the environment and makes the library read it again."""
+    yield
+    from flashmask_b200 import _lib
+    if _lib._lib is not None:
+        _lib.reload_options()

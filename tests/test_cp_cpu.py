@@ -190,6 +190,66 @@ print("rank", rank, "ok")
 """
 
 
+_GLOO_REPLAN = r"""
+import os, sys
+sys.path.insert(0, {root!r})
+import numpy as np, torch, torch.distributed as dist
+from flashmask_b200 import cp, workloads as W
+rank, world = int(sys.argv[1]), 2
+os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT={port!r})
+dist.init_process_group("gloo", rank=rank, world_size=world)
+S = 64                                     # rows per rank = keys per shard
+def need_row(mask, Sq, causal, world):     # CPU stand-in of the device kernel: exact visibility per shard
+    vis = W.dense_visible(mask.numpy(), Sq, causal)[0, 0]
+    return torch.from_numpy(vis.reshape(Sq, world, -1).any(axis=(0, 2)))
+def mask_all():                            # every key visible to every row
+    m = np.zeros((1, 1, world * S, 2), np.int32); m[..., 0] = S; return m
+def mask_own_only():                       # only the own shard visible
+    m = np.zeros((1, 1, world * S, 2), np.int32); m[..., 1] = S
+    m[:, :, rank * S:(rank + 1) * S, 0] = S; m[:, :, rank * S:(rank + 1) * S, 1] = 0; return m
+ex = cp.TorchDistExchange(None)
+gathers = [0]
+orig = ex.all_gather_need
+def counted(row):
+    gathers[0] += 1
+    return orig(row)
+ex.all_gather_need = counted
+state = lambda t: cp.mask_state(t, S, S, 128, 128, ex, need_row_fn=need_row)
+buf = torch.from_numpy(mask_all())
+st1 = state(buf)
+assert st1.plan.need == [[True, True], [True, True]] and st1.owners == [1 - rank] and gathers[0] == 1
+assert state(buf) is st1 and gathers[0] == 1          # same tensor, unchanged: no second all-gather
+# a different mask of the same shape written into the SAME buffer: the plan is rebuilt on every rank
+buf.copy_(torch.from_numpy(mask_own_only()))
+st2 = state(buf)
+assert gathers[0] == 2 and st2.plan.need == [[True, False], [False, True]] and st2.owners == []
+assert st2.rest_mask is None
+# a new tensor object that aliases that storage (what the caching allocator hands to the next step's mask)
+alias = buf.view(buf.shape)
+alias.copy_(torch.from_numpy(mask_all()))
+st3 = state(alias)
+assert gathers[0] == 3 and st3.plan.need == [[True, True], [True, True]]
+# ... and the old tensor object, whose version counter the write moved too, no longer hits its stale entry
+st4 = state(buf)
+assert gathers[0] == 4 and st4.plan.need == [[True, True], [True, True]]
+del alias
+import gc; gc.collect()
+assert all(e[0]() is not None for e in cp._STATE_CACHE.values())   # entries die with their tensors
+dist.barrier(); dist.destroy_process_group()
+print("rank", rank, "ok")
+"""
+
+
+def test_plan_is_rebuilt_when_the_mask_changes_two_ranks_gloo(tmp_path):
+    script = tmp_path / "gloo_replan.py"
+    script.write_text(_GLOO_REPLAN.format(root=ROOT, port=str(31500 + os.getpid() % 2000)))
+    procs = [subprocess.Popen([sys.executable, str(script), str(r)], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=120)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, o
+
+
 def test_plan_exchange_two_ranks_gloo(tmp_path):
     script = tmp_path / "gloo_cp.py"
     script.write_text(_GLOO_SCRIPT.format(root=ROOT, port=str(29500 + os.getpid() % 2000)))

@@ -10,6 +10,7 @@ import torch
 
 from flashmask_b200 import workloads as W
 import flashmask_b200 as fm
+from flashmask_b200 import _lib
 from _util import (assert_lse, assert_parity, make_inputs, naive_lowp, run_oracle, run_product)
 
 pytestmark = pytest.mark.gpu
@@ -23,12 +24,14 @@ def fwd_variant(request):
     old = {n: os.environ.get(n) for n in names}
     for n in names:
         os.environ[n] = request.param
+    _lib.reload_options()
     yield request.param
     for n in names:
         if old[n] is None:
             os.environ.pop(n, None)
         else:
             os.environ[n] = old[n]
+    _lib.reload_options()
 
 
 def _kernel_status():
@@ -215,7 +218,7 @@ def test_launch_order_changes_no_bit(kind, mask_b, hm, persist, monkeypatch):
     persistent backward variant only changes which CTA runs which unit: results are bitwise
     those of the index order, for every mask batch / head broadcast and both backward variants."""
     monkeypatch.setenv("FLASHMASK_B200_PERSIST", persist)
-    monkeypatch.setenv("FLASHMASK_B200_FWD_PERSIST", persist)   # the persistent forward is opt-in
+    _lib.reload_options()
     B, S, Hq, Hkv = 2, 1024, 8, 2
     idx_np, causal = _mask(kind, B, S, S, 33)
     idx_np = np.ascontiguousarray(idx_np[:mask_b]).copy()
@@ -326,6 +329,21 @@ def test_shared_kv_convention():
     want[..., :dv] += dv2.float()
     assert torch.equal(dq, dq2)
     assert (dk.float() - want).abs().max().item() <= 2 ** -6 * max(1.0, want.abs().max().item())
+
+
+def test_aliased_value_keeps_its_own_gradient_below_the_shared_head_dims():
+    """The merge of dV into dK is the reference's convention for (512, 512) and (576, 512) only
+    (flashmask/cute/ops/bwd.py:136-139); at d = 128 a value that aliases the key still gets its dV."""
+    B, S, H, d = 1, 256, 2, 128
+    g = torch.Generator().manual_seed(4)
+    q = torch.randn(B, S, H, d, generator=g).bfloat16().cuda()
+    kv = torch.randn(B, S, H, d, generator=g).bfloat16().cuda()
+    do = torch.randn(B, S, H, d, generator=g).bfloat16().cuda()
+    out, lse = fm._flash_attn_fwd(q, kv, kv, None, causal=True)
+    dq, dk, dv, _ = fm._flash_attn_bwd(q, kv, kv, out, do, lse, None, causal=True)
+    dq2, dk2, dv2, _ = fm._flash_attn_bwd(q, kv, kv.clone(), out, do, lse, None, causal=True)
+    assert float(dv.abs().max()) > 0.0
+    assert torch.equal(dk, dk2) and torch.equal(dv, dv2) and torch.equal(dq, dq2)
 
 
 @pytest.mark.parametrize("d", [64, 128])

@@ -17,6 +17,7 @@ import pytest
 import torch
 
 import flashmask_b200 as fm
+from flashmask_b200 import _lib
 from flashmask_b200 import workloads as W
 
 pytestmark = pytest.mark.gpu
@@ -90,6 +91,7 @@ def test_tcgen05_and_warp_mma_kernels_agree(name, d, monkeypatch):
     a = _fwd_bwd(w, q, k, v, do, idx)
     monkeypatch.setenv("FLASHMASK_B200_FWD", "mma")
     monkeypatch.setenv("FLASHMASK_B200_BWD", "mma")
+    _lib.reload_options()
     b = _fwd_bwd(w, q, k, v, do, idx)
     fin = torch.isfinite(a[1])
     assert torch.equal(fin, torch.isfinite(b[1]))

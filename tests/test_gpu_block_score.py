@@ -13,6 +13,7 @@ import pytest
 import torch
 
 import flashmask_b200 as fm
+from flashmask_b200 import _lib
 import oracle
 
 pytestmark = pytest.mark.gpu
@@ -53,6 +54,7 @@ def _check(got, ref, d, scale=None):
 def variant(request, monkeypatch):
     """Head dims up to 128 have two forward kernel families, both with the side output."""
     monkeypatch.setenv("FLASHMASK_B200_FWD", request.param)
+    _lib.reload_options()
     return request.param
 
 

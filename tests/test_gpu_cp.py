@@ -191,3 +191,53 @@ def test_ipo_partition_end_to_end(cpn):
     assert sorted(order) == list(range(S // chunk)) and all(len(b) == S // chunk // cpn for b in buckets)
     load = lambda bs: max(sum(w for w, _ in b) for b in bs)
     assert load(buckets) <= load(heap_buckets)
+
+
+def test_unneeded_shards_are_never_read_nan_poisoned_buffers():
+    """A shard no row of a rank sees is masked by a MIX of columns (LTS = 0 next to UTE = Sq), so
+    the per-tile reductions alone cannot prove its tiles empty (lts_max = Sq, ute_min = 0) and the
+    attention kernel would run them with the element mask: P = 0 times whatever the buffer holds.
+    The remote buffer therefore has no place for such a shard at all.  The receive buffers are
+    filled with NaN before the pulled shards are copied in; nothing of it may reach the outputs,
+    and the result is the single-GPU operator's."""
+    cpn, S_l, Hq, Hkv = 4, 512, 4, 2
+    S = cpn * S_l
+    # Column c of shard o is visible to the rows [UTE, LTS) (non-causal 2-column form):
+    #   odd columns: the rows of rank o;  even columns of shards 2, 3: the rows of rank 0;
+    #   even columns of shard 0: the rows of ranks 0 and 1;  even columns of shard 1: rank 1.
+    # Ranks 1 and 2 then see shards 2 / 3 (rank 2: shard 3) as a mix of columns masked from
+    # below (visible rows lie before theirs) and from above (after theirs), and need none of them.
+    idx_np = np.zeros((1, 1, S, 2), dtype=np.int32)
+    for c in range(S):
+        o = c // S_l
+        if c % 2 == 0 and o >= 2:
+            lo, hi = 0, S_l
+        elif c % 2 == 0 and o == 0:
+            lo, hi = 0, 2 * S_l
+        else:
+            lo, hi = o * S_l, (o + 1) * S_l
+        idx_np[0, 0, c] = (hi, lo)
+    want_need = [[True, False, True, True], [True, True, False, False], [False, False, True, False],
+                 [False, False, False, True]]
+    idx = torch.from_numpy(idx_np).cuda()
+    g = torch.Generator().manual_seed(5)
+    q, k, v, do = (torch.randn(1, S, h, 128, generator=g).bfloat16().cuda() for h in (Hq, Hkv, Hkv, Hq))
+    qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+    out_ref, lse_ref = fm.flashmask_attention(qg, kg, vg, idx, causal=False, return_lse=True)
+    out_ref.backward(do)
+    # identity partition (rank r owns rows / keys [r*S_l, (r+1)*S_l)); local masks: row bounds
+    # shifted into the rank's local rows and clamped
+    sc = lambda t: [t[:, r * S_l:(r + 1) * S_l].contiguous() for r in range(cpn)]
+    locals_ = []
+    for r in range(cpn):
+        loc = np.clip(idx_np.astype(np.int64) - r * S_l, 0, S_l).astype(np.int32)
+        locals_.append(torch.from_numpy(loc).cuda())
+        assert cp.shard_need_row(locals_[-1], S_l, False, cpn).cpu().tolist() == want_need[r], r
+    far = locals_[1][0, 0, 2 * S_l:3 * S_l].cpu().numpy()      # rank 1's view of shard 2: mixed
+    assert (far[0::2] == 0).all() and (far[1::2] == S_l).all()
+    outs, lses, dqs, dks, dvs, _ = cp.emulate_cp(sc(q), sc(k), sc(v), sc(do), locals_, poison=float("nan"))
+    for name, parts, ref in (("out", outs, out_ref), ("dq", dqs, qg.grad), ("dk", dks, kg.grad), ("dv", dvs, vg.grad)):
+        a = torch.cat(parts, dim=1)
+        assert not torch.isnan(a.float()).any(), name
+        err = (a.float() - ref.float()).abs().max().item()
+        assert err <= 2 ** -7 * cpn * max(1.0, ref.float().abs().max().item()), (name, err)
