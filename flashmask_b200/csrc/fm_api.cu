@@ -38,6 +38,9 @@ int fwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s
 bool bwd_sm100_supported(const fm_attn_args* a);
 int bwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s);
 int bwd_sm100_persist_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s);
+int bwd_sm100_fused_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s);
+int bwd_sm100_fused_status(int* out, bool reset);
+size_t bwd_sm100_fused_accum_bytes(const fm_attn_args* a);
 int bwd_sm100_persist_status(int* out, bool reset);
 size_t bwd_sm100_workspace_bytes(const fm_attn_args* a);
 
@@ -51,13 +54,15 @@ static inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 // the host asks through fm_reload_options): no entry point touches the environment per call.
 //   FLASHMASK_B200_FWD=mma       forward on the warp-MMA kernels for every head dim
 //   FLASHMASK_B200_BWD=mma       backward on the warp-MMA kernels for every head dim
+//   FLASHMASK_B200_BWD=split     tcgen05 backward as two kernels (dK/dV + dQ) even when the call
+//                                did not ask for deterministic gradients
 //   FLASHMASK_B200_PERSIST=0     tcgen05 backward: one unit per CTA even with launch tables
 //   FLASHMASK_B200_CLASSES=n     work classes of the launch tables (1..8)
-struct Options { bool fwd_mma, bwd_mma, bwd_persist; int order_classes; };
+struct Options { bool fwd_mma, bwd_mma, bwd_split, bwd_persist; int order_classes; };
 static Options read_options() {
-  Options o{false, false, true, 0};
+  Options o{false, false, false, true, 0};
   if (const char* e = getenv("FLASHMASK_B200_FWD")) o.fwd_mma = strcmp(e, "mma") == 0;
-  if (const char* e = getenv("FLASHMASK_B200_BWD")) o.bwd_mma = strcmp(e, "mma") == 0;
+  if (const char* e = getenv("FLASHMASK_B200_BWD")) { o.bwd_mma = strcmp(e, "mma") == 0; o.bwd_split = strcmp(e, "split") == 0; }
   if (const char* e = getenv("FLASHMASK_B200_PERSIST")) o.bwd_persist = !(e[0] == '0' && e[1] == 0);
   if (const char* e = getenv("FLASHMASK_B200_CLASSES")) o.order_classes = atoi(e);
   return o;
@@ -153,12 +158,25 @@ static bool bwd_uses_sm100(int d, int dv) {
   return !g_opt.bwd_mma;
 }
 
+// The one-kernel backward (five GEMMs per tile pair, dQ summed into an fp32 accumulator in an order
+// that is not fixed) serves the tcgen05 head dims whenever the call does not ask for deterministic
+// gradients; the two-kernel variant gives every output element one owner and a fixed order.
+static bool bwd_uses_fused(const fm_attn_args* a) {
+  return bwd_uses_sm100(a->d, a->dv) && !a->deterministic && !g_opt.bwd_split;
+}
+
 // preprocess -> main kernels of the selected variant -> dsink, on one stream
 static int run_bwd_kernels(const fm_attn_args* a, const AttnKParams& p, cudaStream_t s) {
   int rc = bwd_preprocess_launch(p, a->dtype, s);
   if (rc != FM_OK) return rc;
   if (bwd_uses_sm100(a->d, a->dv)) {
     FM_REQUIRE(bwd_sm100_supported(a), FM_ERR_INVALID_ARGUMENT, "backward: q/k/v/d_o must be 16-byte aligned");
+    if (p.dq_accum) {
+      rc = bwd_sm100_fused_launch(p, a, s);
+      if (rc != FM_OK) return rc;
+      if (a->sink) rc = bwd_dsink_launch(p, s);
+      return rc;
+    }
     // With launch tables (a mask tensor) the persistent variant walks them; without, one unit per CTA.
     // Measured on six 8K-32K masks the persistent variant is 3-14 % faster where units are short
     // (documents, windows) and 3-5 % slower where every unit is hundreds of items long (its main loop
@@ -330,10 +348,16 @@ extern "C" int fm_launch_orders(const fm_attn_args* a, int32_t* out_fwd, int32_t
   return launch_order_build(md, 128, jobs, n, (cudaStream_t)stream);
 }
 
+// Workspace layout: rowsum(O dO) and LSE*log2e, one float each per (batch, q head, padded row),
+// then (one-kernel backward only) the fp32 dQ accumulator, 256-byte aligned.
+static size_t bwd_row_stat_bytes(const fm_attn_args* a) {
+  const size_t rows = (size_t)a->B * a->Hq * round_up(a->Sq, 128);
+  return (2 * rows * sizeof(float) + 255) & ~(size_t)255;
+}
+
 extern "C" size_t fm_bwd_workspace_bytes(const fm_attn_args* a) {
   if (!a || a->B <= 0 || a->Hq <= 0 || a->Sq <= 0) return 0;
-  const size_t rows = (size_t)a->B * a->Hq * round_up(a->Sq, 128);
-  return 2 * rows * sizeof(float);
+  return bwd_row_stat_bytes(a) + (bwd_uses_fused(a) ? bwd_sm100_fused_accum_bytes(a) : 0);
 }
 
 extern "C" int fm_bwd(const fm_attn_args* a, void* stream) {
@@ -360,6 +384,8 @@ extern "C" int fm_bwd(const fm_attn_args* a, void* stream) {
   const size_t rows = (size_t)a->B * a->Hq * p.Sq_r;
   p.dpsum = reinterpret_cast<float*>(a->workspace);
   p.lse_log2 = p.dpsum + rows;
+  if (bwd_uses_fused(a))
+    p.dq_accum = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a->workspace) + bwd_row_stat_bytes(a));
   cudaStream_t s = (cudaStream_t)stream;
   attach_bwd_tables(a, &p);
   return run_bwd_kernels(a, p, s);
@@ -372,9 +398,11 @@ extern "C" int fm_kernel_status(int* status, int reset) {
   if (rc != FM_OK) return rc;
   rc = bwd_sm100_status(&bw, reset != 0);
   if (rc != FM_OK) return rc;
-  int bp = 0;
+  int bp = 0, bf = 0;
   rc = bwd_sm100_persist_status(&bp, reset != 0);
-  *status = f ? f : (bw ? bw : bp);
+  if (rc != FM_OK) return rc;
+  rc = bwd_sm100_fused_status(&bf, reset != 0);
+  *status = f ? f : (bw ? bw : (bp ? bp : bf));
   return rc;
 }
 

@@ -15,7 +15,7 @@ from typing import Optional, Tuple, Union
 
 import torch
 
-from .ops import _flash_attn_bwd, _flash_attn_fwd, fwd_tile_shape, prepare_mask
+from .ops import _check_shapes, _flash_attn_bwd, _flash_attn_fwd, fwd_tile_shape, prepare_mask
 
 __all__ = ["flashmask_attention", "FlashMaskFunc", "sliding_window_indices"]
 
@@ -26,6 +26,9 @@ class FlashMaskFunc(torch.autograd.Function):
                 deterministic):
         # the mask is scanned once: forward and backward share its per-K-tile reductions and the
         # launch tables whenever their kernel variants tile the keys alike
+        if not q.is_cuda:
+            raise RuntimeError("flashmask_b200 runs on CUDA (sm_100a) tensors only; there is no CPU path")
+        _check_shapes(q, k, v, startend_row_indices, causal)
         info = None
         if startend_row_indices is not None:
             tm, tn = fwd_tile_shape(q.shape[-1], v.shape[-1])

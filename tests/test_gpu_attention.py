@@ -16,14 +16,16 @@ from _util import (assert_lse, assert_parity, make_inputs, naive_lowp, run_oracl
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=["sm100", "mma"])
+@pytest.fixture(params=["sm100", "split", "mma"])
 def fwd_variant(request):
-    """d = dv = 128 has two kernel families: the tcgen05 ones (default) and the
-    warp-MMA ones; FLASHMASK_B200_FWD / FLASHMASK_B200_BWD select per call."""
+    """Head dims up to 128 have two kernel families, the tcgen05 ones (default) and the warp-MMA
+    ones, and the tcgen05 backward has a one-kernel variant (default when the call does not ask for
+    deterministic gradients) and a two-kernel one ("split"); FLASHMASK_B200_FWD / FLASHMASK_B200_BWD
+    select them."""
     names = ("FLASHMASK_B200_FWD", "FLASHMASK_B200_BWD")
     old = {n: os.environ.get(n) for n in names}
-    for n in names:
-        os.environ[n] = request.param
+    os.environ["FLASHMASK_B200_FWD"] = "mma" if request.param == "mma" else "sm100"
+    os.environ["FLASHMASK_B200_BWD"] = request.param
     _lib.reload_options()
     yield request.param
     for n in names:

@@ -113,15 +113,22 @@ def test_sampled_rows_and_key_columns(name, hk, stats):
     bd = _bounds(w, b)
     rng = np.random.default_rng(7)
     rows = _sample_rows(rng, w, b, 320)
+    # the rule is applied to the sampled rows of both heads together, as the reference's test applies
+    # it to whole tensors: the maxima of a few hundred rows of one head alone are too noisy a statistic
+    parts = {n: ([], [], []) for n in ("out", "dq")}
     for g in sorted({0, G - 1}):
         h = hk * G + g
         s = None if sink is None else float(sink[h])
         ref = oracle.attention_rows(q[b, :, h], k[b, :, hk], v[b, :, hk], do[b, :, h], bd, w.causal, s,
                                     rows=rows)
         lp = lowp_rows(qd[b, :, h], kd[b, :, hk], vd[b, :, hk], dod[b, :, h], bd, w.causal, s, rows=rows)
-        assert_close_rule(got["out"][b, rows, h], ref["out"], lp["out"], f"{name} out h{h}")
-        assert_close_rule(got["dq"][b, rows, h], ref["dq"], lp["dq"], f"{name} dq h{h}")
+        for n in parts:
+            parts[n][0].append(got[n][b, rows, h].float().cpu())
+            parts[n][1].append(ref[n])
+            parts[n][2].append(lp[n].float().cpu())
         _check_lse(got["lse"][b, h, rows], ref["lse"], f"{name} h{h}")
+    for n, (a, r_, l_) in parts.items():
+        assert_close_rule(torch.cat(a), torch.cat(r_), torch.cat(l_), f"{name} {n}")
     # row statistics of every q head of the group, all rows
     hs = slice(hk * G, hk * G + G)
     if stats == "oracle":
