@@ -115,7 +115,12 @@ typedef struct fm_attn_args {
   int32_t dtype;      /* FM_DTYPE_*                                          */
   int32_t mask_B;     /* batch of the mask tensor: B or 1 (broadcast)        */
   int32_t tile_m, tile_n; /* tile shape `minmax` was prepared for            */
-  int32_t deterministic;  /* backward only                                   */
+  int32_t deterministic;  /* backward only: 1 = fixed summation order, bitwise
+                             reproducible gradients (two tcgen05 kernels, one
+                             owner per output element); 0 = the one-kernel
+                             backward may be used (d = dv = 64 or 128), whose dQ
+                             is summed by reductions in an order that is not
+                             fixed                                            */
   int32_t reserved0;
   float softmax_scale;
   float reserved1;
@@ -255,7 +260,14 @@ FM_API int fm_selftest_bounded_wait(int budget_us, void* stream);
  * (flash_bwd_preprocess.py:184-342), main (flash_bwd_sm100.py:1435-),
  * postprocess (flash_bwd_postprocess.py:309-) and dsink
  * (flash_bwd_sink.py:67-114).  `workspace` must hold
- * fm_bwd_workspace_bytes(args) bytes; its contents need no initialisation. */
+ * fm_bwd_workspace_bytes(args) bytes; its contents need no initialisation.
+ * The size depends on args->deterministic: the one-kernel backward
+ * (flash_bwd_sm100.py:129-140: S, dP, dV, dK and dQ of a tile pair computed once)
+ * adds an fp32 dQ accumulator [B, Hq, roundup(Sq,128), 64|128] behind the row
+ * statistics, the role of the reference's dq_accum (ops/bwd.py:366-383), which it
+ * clears itself and rounds into dq with one more small kernel (the reference's
+ * postprocess, flash_bwd_postprocess.py).  Ask for the size with the same
+ * args->deterministic the call will carry. */
 FM_API size_t fm_bwd_workspace_bytes(const fm_attn_args* args);
 FM_API int fm_bwd(const fm_attn_args* args, void* stream);
 
