@@ -333,6 +333,34 @@ def test_shared_kv_convention():
     assert (dk.float() - want).abs().max().item() <= 2 ** -6 * max(1.0, want.abs().max().item())
 
 
+@pytest.mark.parametrize("deterministic", [True, False])
+def test_four_column_mask_long_lists_both_backward_variants(deterministic):
+    """A 4-column mask whose units carry far more than 64 work items (S = 8192: up to 128 half
+    tiles per unit and q head), through the two-kernel and the one-kernel backward: the case on
+    which an MMA issue order that let the second score GEMM of item k+2 overwrite the P^T / dS^T
+    of item k once gave wrong gradients."""
+    B, S, Hq, Hkv, d = 1, 8192, 2, 1, 128
+    rng = np.random.default_rng(77)
+    idx_np, causal = W.four_column_bands(B, S, S, rng)
+    q, k, v, do, _ = make_inputs(B, S, S, Hq, Hkv, d, d, 77)
+    idx = torch.from_numpy(np.ascontiguousarray(idx_np).copy()).cuda()
+    got = run_product(q.cuda(), k.cuda(), v.cuda(), do.cuda(), idx, causal, None, deterministic=deterministic)
+    import oracle
+    from _util import assert_close_rule, lowp_rows
+    bd = idx_np[0, 0]
+    dk_ref = torch.zeros(S, d); dv_ref = torch.zeros(S, d); dk_lp = torch.zeros(S, d); dv_lp = torch.zeros(S, d)
+    for h in range(Hq):
+        ref = oracle.attention_rows(q[0, :, h], k[0, :, 0], v[0, :, 0], do[0, :, h], bd, causal)
+        lp = lowp_rows(q[0, :, h].cuda(), k[0, :, 0].cuda(), v[0, :, 0].cuda(), do[0, :, h].cuda(), bd, causal, None)
+        assert_close_rule(got["dq"][0, :, h], ref["dq"], lp["dq"], f"dq h{h}")
+        assert_close_rule(got["out"][0, :, h], ref["out"], lp["out"], f"out h{h}")
+        dk_ref += ref["dk"]; dv_ref += ref["dv"]
+        dk_lp += lp["dk"].float().cpu(); dv_lp += lp["dv"].float().cpu()
+    assert_close_rule(got["dk"][0, :, 0], dk_ref, dk_lp, "dk")
+    assert_close_rule(got["dv"][0, :, 0], dv_ref, dv_lp, "dv")
+    assert _kernel_status() == 0
+
+
 def test_aliased_value_keeps_its_own_gradient_below_the_shared_head_dims():
     """The merge of dV into dK is the reference's convention for (512, 512) and (576, 512) only
     (flashmask/cute/ops/bwd.py:136-139); at d = 128 a value that aliases the key still gets its dV."""
