@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libflashmask_b200.so")
 FM_OK = 0
 FM_DTYPE_BF16, FM_DTYPE_FP16 = 0, 1
 FM_ORDER_FWD, FM_ORDER_BWD_DQ, FM_ORDER_BWD_DKDV = 0, 1, 2
+FM_BWD_DQ_CARRY, FM_BWD_DQ_LEAVE = 1, 2
 TILE_SKIP, TILE_PARTIAL, TILE_FULL = 0, 1, 2
 
 I64x3 = C.c_int64 * 3
@@ -28,7 +29,7 @@ class AttnArgs(C.Structure):
         ("Hkv", C.c_int32), ("Hm", C.c_int32), ("d", C.c_int32), ("dv", C.c_int32),
         ("ncols", C.c_int32), ("causal", C.c_int32), ("dtype", C.c_int32),
         ("mask_B", C.c_int32), ("tile_m", C.c_int32), ("tile_n", C.c_int32),
-        ("deterministic", C.c_int32), ("reserved0", C.c_int32),
+        ("deterministic", C.c_int32), ("bwd_flags", C.c_int32),
         ("softmax_scale", C.c_float), ("reserved1", C.c_float),
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p),
         ("o", C.c_void_p), ("lse", C.c_void_p),
@@ -62,6 +63,7 @@ SIGNATURES = {
     "fm_launch_orders": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "fm_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(AttnArgs)]),
     "fm_bwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
+    "fm_bwd_accumulates": (C.c_int, [C.POINTER(AttnArgs)]),
     "fm_kernel_status": (C.c_int, [C.POINTER(C.c_int), C.c_int]),
     "fm_selftest_bounded_wait": (C.c_int, [C.c_int, C.c_void_p]),
     "fm_bwd_static_scratch": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
@@ -75,6 +77,8 @@ SIGNATURES = {
                                       C.c_int, C.c_void_p, C.c_void_p]),
     "fm_cp_merge_partial": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
                                       C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "fm_cp_merge_two": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                                  C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "fm_cp_accumulate": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
     "fm_cp_cast": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
     "fm_cp_reduce_partials": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_void_p, C.c_int64, C.c_int,

@@ -354,25 +354,35 @@ def cp_forward(q, k, v, remote: Optional[RemoteKV], st: CPMaskState, softmax_sca
     if not parts:
         return (torch.zeros((B, Sq, Hq, dv), dtype=q.dtype, device=q.device),
                 torch.full((B, Hq, Sq), float("-inf"), dtype=torch.float32, device=q.device))
-    acc = torch.empty((B, Sq, Hq, dv), dtype=torch.float32, device=q.device)
+    (o_a, lse_a), (o_b, lse_b) = parts
     lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device)
-    _merge(acc, lse, parts[0][0], parts[0][1], True)
-    _merge(acc, lse, parts[1][0], parts[1][1], False)
-    out = _cast(acc, q)
+    # both partials are contiguous [B, Sq, Hq, dv]; the merged rows overwrite the first one
+    _lib.check(_lib.load().fm_cp_merge_two(o_a.data_ptr(), lse_a.data_ptr(), o_b.data_ptr(), lse_b.data_ptr(),
+                                           o_a.data_ptr(), lse.data_ptr(), B, Sq, Hq, dv, _dtype_code(o_a),
+                                           _stream(o_a)), "fm_cp_merge_two")
     _mark("fwd_merge")
-    return out, lse
+    return o_a, lse
 
 
-def cp_backward_remote(q, remote, out, dout, lse, st: CPMaskState, softmax_scale, deterministic):
-    """Gradients of the remote call: (dq_remote, dk_all_remote, dv_all_remote)."""
+def cp_backward_remote(q, remote, out, dout, lse, st: CPMaskState, softmax_scale, deterministic, dq_chain=None):
+    """Gradients of the remote call: (dq_remote, dk_all_remote, dv_all_remote).  With ``dq_chain``
+    (and the own-shard call still to come) dq may stay in the chain's accumulator: dq_remote is None."""
     dq, dk, dv, _ = _flash_attn_bwd(q, remote.k, remote.v, out, dout, lse, st.rest_mask, softmax_scale=softmax_scale,
-                                    causal=False, deterministic=deterministic, mask_info=st.rest_info)
+                                    causal=False, deterministic=deterministic, mask_info=st.rest_info,
+                                    dq_chain=dq_chain)
     return dq, dk, dv
 
 
-def cp_backward_own(q, k, v, out, dout, lse, st: CPMaskState, softmax_scale, sink, deterministic):
+def cp_backward_own(q, k, v, out, dout, lse, st: CPMaskState, softmax_scale, sink, deterministic, dq_chain=None):
     return _flash_attn_bwd(q, k, v, out, dout, lse, st.own_mask, softmax_scale=softmax_scale, causal=False,
-                           learnable_sink=sink, deterministic=deterministic, mask_info=st.own_info)
+                           learnable_sink=sink, deterministic=deterministic, mask_info=st.own_info,
+                           dq_chain=dq_chain)
+
+
+def _dq_chain(n_calls: int):
+    """Chain record for the backward calls of one rank: with two calls (pulled shards, then own shard) the
+    first leaves its dQ in the fp32 accumulator of the one-kernel backward and the second rounds the sum."""
+    return {"last": False} if n_calls == 2 else None
 
 
 def _sum_dq(dq_a, dq_b):
@@ -380,10 +390,7 @@ def _sum_dq(dq_a, dq_b):
         return dq_b
     if dq_b is None:
         return dq_a
-    acc = torch.empty(dq_a.shape, dtype=torch.float32, device=dq_a.device)
-    _accumulate(acc, dq_a, True)
-    _accumulate(acc, dq_b, False)
-    return _cast(acc, dq_a)
+    return _reduce_partials([dq_a, dq_b])      # fp32 sum of the two, rounded once
 
 
 def _dsink_only(q, k, v, out, dout, lse, sink, softmax_scale):
@@ -430,9 +437,10 @@ class _CPFunc(torch.autograd.Function):
         dq_r = None
         send, ready = {}, None
         recv = {t: [torch.empty_like(k), torch.empty_like(v)] for t in plan.pushes()}
+        chain = _dq_chain(int(bool(st.owners)) + int(need_own))
         _mark("bwd:begin")
         if st.owners:
-            dq_r, dk_all, dv_all = cp_backward_remote(q, remote, out, dout, lse, st, ctx.softmax_scale, det)
+            dq_r, dk_all, dv_all = cp_backward_remote(q, remote, out, dout, lse, st, ctx.softmax_scale, det, chain)
             send = {o: [remote.slice_of(dk_all, o).contiguous(), remote.slice_of(dv_all, o).contiguous()]
                     for o in plan.pulls()}
             _mark("bwd_remote")
@@ -441,7 +449,9 @@ class _CPFunc(torch.autograd.Function):
         dq_o = dsink = None
         own = None
         if need_own:
-            dq_o, dk_o, dv_o, dsink = cp_backward_own(q, k, v, out, dout, lse, st, ctx.softmax_scale, sink, det)
+            if chain is not None:
+                chain["last"] = True
+            dq_o, dk_o, dv_o, dsink = cp_backward_own(q, k, v, out, dout, lse, st, ctx.softmax_scale, sink, det, chain)
             own = (dk_o, dv_o)
             _mark("bwd_own")
         elif sink is not None:
@@ -543,14 +553,17 @@ def emulate_cp(qs, ks, vs, douts, local_masks, softmax_scale=None, sink=None, de
     dqs, contrib, dsinks = [], {o: {} for o in range(world)}, []
     for r in range(world):
         dq_r = dq_o = ds = None
+        chain = _dq_chain(int(bool(states[r].owners)) + int(need[r][r]))
         if states[r].owners:
             dq_r, dk_all, dv_all = cp_backward_remote(qs[r], remotes[r], outs[r], douts[r], lses[r], states[r],
-                                                      softmax_scale, deterministic)
+                                                      softmax_scale, deterministic, chain)
             for o in plans[r].pulls():
                 contrib[o][r] = (remotes[r].slice_of(dk_all, o), remotes[r].slice_of(dv_all, o))
         if need[r][r]:
+            if chain is not None:
+                chain["last"] = True
             dq_o, dk_o, dv_o, ds = cp_backward_own(qs[r], ks[r], vs[r], outs[r], douts[r], lses[r], states[r],
-                                                   softmax_scale, sink, deterministic)
+                                                   softmax_scale, sink, deterministic, chain)
             contrib[r][r] = (dk_o, dv_o)
         elif sink is not None:
             ds = _dsink_only(qs[r], ks[r], vs[r], outs[r], douts[r], lses[r], sink, softmax_scale)

@@ -358,9 +358,19 @@ static size_t bwd_row_stat_bytes(const fm_attn_args* a) {
   return (2 * rows * sizeof(float) + 255) & ~(size_t)255;
 }
 
+// One-kernel backward: the statistics once more as 16-bit GEMM operands, 2 x 16 bytes per row.
+static size_t bwd_stat_operand_bytes(const fm_attn_args* a) {
+  return (size_t)a->B * a->Hq * round_up(a->Sq, 128) * 32;
+}
+
 extern "C" size_t fm_bwd_workspace_bytes(const fm_attn_args* a) {
   if (!a || a->B <= 0 || a->Hq <= 0 || a->Sq <= 0) return 0;
-  return bwd_row_stat_bytes(a) + (bwd_uses_fused(a) ? bwd_sm100_fused_accum_bytes(a) : 0);
+  return bwd_row_stat_bytes(a) +
+         (bwd_uses_fused(a) ? bwd_sm100_fused_accum_bytes(a) + bwd_stat_operand_bytes(a) : 0);
+}
+
+extern "C" int fm_bwd_accumulates(const fm_attn_args* a) {
+  return (a && a->d > 0 && a->dv > 0 && bwd_uses_fused(a)) ? 1 : 0;
 }
 
 extern "C" int fm_bwd(const fm_attn_args* a, void* stream) {
@@ -387,8 +397,13 @@ extern "C" int fm_bwd(const fm_attn_args* a, void* stream) {
   const size_t rows = (size_t)a->B * a->Hq * p.Sq_r;
   p.dpsum = reinterpret_cast<float*>(a->workspace);
   p.lse_log2 = p.dpsum + rows;
-  if (bwd_uses_fused(a))
-    p.dq_accum = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a->workspace) + bwd_row_stat_bytes(a));
+  if (bwd_uses_fused(a)) {
+    uint8_t* w = reinterpret_cast<uint8_t*>(a->workspace) + bwd_row_stat_bytes(a);
+    p.dq_accum = reinterpret_cast<float*>(w);
+    p.stat_s = reinterpret_cast<uint16_t*>(w + bwd_sm100_fused_accum_bytes(a));
+    p.stat_dp = p.stat_s + (size_t)a->B * a->Hq * p.Sq_r * 8;
+    p.bwd_flags = a->bwd_flags;
+  }
   cudaStream_t s = (cudaStream_t)stream;
   attach_bwd_tables(a, &p);
   return run_bwd_kernels(a, p, s);

@@ -10,7 +10,11 @@ struct AttnKParams {
   const void* d_o; void* dq; void* dk; void* dv; float* dsink;
   float* dpsum;     // [B,Hq,Sq_r] fp32 workspace: rowsum(O * dO)
   float* lse_log2;  // [B,Hq,Sq_r] fp32 workspace: LSE * log2(e), -inf -> 0
-  float* dq_accum;  // [B,Hq,Sq_r,d_r] fp32 workspace (atomic dQ path)
+  float* dq_accum;  // [B,Hq,Sq_r,64|128] fp32 workspace (one-kernel backward: dQ summed by reductions)
+  // one-kernel backward only: the row statistics as 16-bit GEMM operands, [B,Hq,Sq_r,8] each:
+  // (-c_hi, -c_lo, 0 x 6) with c = LSE*log2e / scale_log2, and (-d_hi, -d_lo, 0 x 6) with d = rowsum(O dO)
+  uint16_t* stat_s; uint16_t* stat_dp;
+  int bwd_flags;    // FM_BWD_DQ_CARRY: the accumulator holds earlier sums; FM_BWD_DQ_LEAVE: dq is not written
   int64_t q_b, q_s, q_h, k_b, k_s, k_h, v_b, v_s, v_h, o_b, o_s, o_h;
   int64_t do_b, do_s, do_h, dq_b, dq_s, dq_h, dk_b, dk_s, dk_h, dv_b, dv_s, dv_h;
   int B, Sq, Sk, Hq, Hkv, d, dv_dim;

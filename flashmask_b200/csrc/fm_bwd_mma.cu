@@ -425,6 +425,20 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const AttnKParams p
     const int64_t at = ((int64_t)b * p.Hq + hq) * p.Sq_r + row;
     p.dpsum[at] = acc;
     p.lse_log2[at] = lse2;
+    if (p.stat_s) {
+      // the same two values as 16-bit GEMM operands (hi + lo parts, negated): see the one-kernel backward
+      const float c = lse2 / p.scale_log2;
+      float c_hi, c_lo, d_hi, d_lo;
+      if constexpr (IS_BF16) {
+        c_hi = __bfloat162float(__float2bfloat16_rn(c)); c_lo = c - c_hi;
+        d_hi = __bfloat162float(__float2bfloat16_rn(acc)); d_lo = acc - d_hi;
+      } else {
+        c_hi = __half2float(__float2half_rn(c)); c_lo = c - c_hi;
+        d_hi = __half2float(__float2half_rn(acc)); d_lo = acc - d_hi;
+      }
+      *reinterpret_cast<uint4*>(p.stat_s + at * 8) = make_uint4(pack2<IS_BF16>(-c_hi, -c_lo), 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(p.stat_dp + at * 8) = make_uint4(pack2<IS_BF16>(-d_hi, -d_lo), 0u, 0u, 0u);
+    }
   }
 }
 

@@ -45,13 +45,20 @@ struct BwdFusedCfg {
   static constexpr int HALF_BYTES = 2 * SUB64;         // one operand of a half tile
   static constexpr int SLOT_BYTES = 2 * HALF_BYTES;    // Q half + dO half
   static constexpr int DS_BYTES = 128 * 128;           // dS^T: 128 keys x 64 queries bf16
-  static constexpr int AUX_BYTES = 512;                // LSE*log2e and rowsum(O dO) of 64 rows
+  static constexpr int AUX_BYTES = 2048;               // two 64-row x 16-byte statistics operands (see STAT below)
   static constexpr int OFF_STAT = 0;                   // K tile, then V tile
   static constexpr int OFF_RING = OFF_STAT + 2 * TILE_BYTES;
   static constexpr int OFF_DS = OFF_RING + NSLOT * SLOT_BYTES;          // one buffer per item parity
-  static constexpr int OFF_AUX = OFF_DS + 2 * DS_BYTES;
-  static constexpr int NAUX = 4;                       // row statistics have a ring of their own (see B_AFULL)
-  static constexpr int OFF_LIST = OFF_AUX + NAUX * AUX_BYTES;           // two lists of 16-bit entries: units alternate
+  // STAT: the per-query statistics enter through the GEMMs.  S^T = K Q^T gets one more k-step whose A is a
+  // tile of ones and whose B holds, per query, (-c_hi, -c_lo, 0, ...) with c = LSE*log2e / scale_log2 split
+  // into two 16-bit parts: the accumulator then already holds S - c, and P = exp2(scale_log2 * (S - c)) needs
+  // no per-column value in the compute warps.  dP^T = V dO^T likewise gets (-d_hi, -d_lo) with d = rowsum(O dO).
+  // Both operands are K-major without swizzle: 8-row x 16-byte core matrices; the second half of K (columns
+  // 8..15) of A reads the ones again, that of B a block of zeros.
+  static constexpr int OFF_AUX = OFF_DS + 2 * DS_BYTES;                 // per ring slot: S statistics, dP statistics
+  static constexpr int OFF_ONES = OFF_AUX + NSLOT * AUX_BYTES;          // 17 core matrices of ones (2176 bytes)
+  static constexpr int OFF_ZEROS = OFF_ONES + 2176;                     // 8 core matrices of zeros (1 KB)
+  static constexpr int OFF_LIST = OFF_ZEROS + 1024;                     // two lists of 16-bit entries: units alternate
   static constexpr int OFF_STAGE = OFF_LIST + 2 * LIST_MAX * 2;         // reductions of the unit's K tile (8 x 4 ints)
   static constexpr int EPI_BYTES = 32 * 64;                             // per epilogue warp: 32 rows x 32 bf16 columns
   static constexpr int RROWS = 16;                                      // dQ staging: 16 query rows x 32 floats per buffer,
@@ -68,12 +75,7 @@ struct BwdFusedCfg {
   // ... and unit-level ones (phases follow the unit counter of the CTA)
   static constexpr int B_STAT = B_DQFREE + 1, B_VFREE = B_STAT + 1, B_KFREE = B_VFREE + 1, B_ACC = B_KFREE + 1,
                        B_ACCFREE = B_ACC + 1, B_INFOREADY = B_ACCFREE + 1, B_INFOFREE = B_INFOREADY + 2,
-                       B_COORD = B_INFOFREE + 2, B_FETCHGO = B_COORD + 2,
-  // Row statistics of item kk land in aux slot kk % 4 and complete B_AFULL + kk % 4: with four slots a
-  // compute warpgroup (every other item) meets each of its two barriers in consecutive phases, which the
-  // three-slot operand ring could not give it.  A slot is reloaded for item kk+4 only after the GEMMs
-  // of item kk+1 have completed, long after item kk's warpgroup has read it: no "empty" barrier is needed.
-                       B_AFULL = B_FETCHGO + 1, B_COUNT = B_AFULL + NAUX;
+                       B_COORD = B_INFOFREE + 2, B_FETCHGO = B_COORD + 2, B_COUNT = B_FETCHGO + 1;
   static constexpr int FETCH_AHEAD = 16;   // items left in a unit when the next one is claimed
   static_assert(B_COUNT <= 32, "barrier storage");
   static_assert(RBUF_BYTES >= EPI_BYTES && OFF_EPI % 128 == 0, "epilogue staging fits the dQ staging");
@@ -142,6 +144,13 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 template <int N>
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// Shared-memory descriptor of a K-major operand WITHOUT swizzle: 8-row x 16-byte core matrices; `lbo` = bytes
+// between the two core matrices of one k-step (K columns 0..7 and 8..15), `sbo` = bytes between 8-row groups.
+__device__ __forceinline__ uint64_t make_sdesc_noswz(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46);
+}
 
 // Four k-steps (K = 64) of D[tmem] (+)= A[smem] * B[smem]: A K-major (advances 32 bytes per
 // step inside its 128-byte rows), B MN-major (advances 16 rows = 2048 bytes per step).
@@ -222,9 +231,15 @@ bwd_sm100_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
   const int n_table = p.dkdv_ncta;
 
   if (tid == 0) misc[4] = 0;
+  {
+    // constant operands of the statistics k-step: ones (1.0 in the kernel's 16-bit type) and zeros
+    const uint32_t one2 = IS_BF16 ? 0x3F803F80u : 0x3C003C00u;
+    for (int x = tid; x < 2176 / 4; x += Cfg::NTHREADS) reinterpret_cast<uint32_t*>(smem + Cfg::OFF_ONES)[x] = one2;
+    for (int x = tid; x < 1024 / 4; x += Cfg::NTHREADS) reinterpret_cast<uint32_t*>(smem + Cfg::OFF_ZEROS)[x] = 0u;
+    fence_proxy_async_smem();
+  }
   if (warp == 8 && lane == 0) {
     for (int i = 0; i < Cfg::NSLOT; ++i) { mbar_init(bar(Cfg::B_RFULL + i), 1); mbar_init(bar(Cfg::B_REMPTY + i), 1); }
-    for (int i = 0; i < Cfg::NAUX; ++i) mbar_init(bar(Cfg::B_AFULL + i), 1);
     for (int h = 0; h < 2; ++h) {
       mbar_init(bar(Cfg::B_GFULL + h), 1); mbar_init(bar(Cfg::B_TFULL + h), 4); mbar_init(bar(Cfg::B_DSFREE + h), 1);
       mbar_init(bar(Cfg::B_INFOREADY + h), 1); mbar_init(bar(Cfg::B_INFOFREE + h), 15);
@@ -381,13 +396,9 @@ bwd_sm100_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
         const uint32_t e = list[k % cnt];
         const int idx = (int)(e & 0xFFFu);
         const uint32_t flags = e >> 12;
-        const int aslot = kk % Cfg::NAUX;
-        ok = __all_sync(0xffffffffu, mbar_wait_parked(bar(Cfg::B_AFULL + aslot), (uint32_t)(kk / Cfg::NAUX) & 1u, wc));
-        if (!ok) break;
         ok = __all_sync(0xffffffffu, mbar_wait_parked(bar(Cfg::B_GFULL + wg), (uint32_t)(kk >> 1) & 1u, wc));
         if (!ok) break;
         tc_fence_after();
-        const uint8_t* aux = smem + Cfg::OFF_AUX + aslot * Cfg::AUX_BYTES;
         const uint32_t NEG = 0xff800000u;
         // 64 score columns; once they are in registers the score buffers belong to the next item
         uint32_t sr[2][32], dr[2][32];
@@ -419,23 +430,12 @@ bwd_sm100_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
             for (int c = 0; c < 16; ++c)
               if (mbits & (1u << c)) sr[hc][c0 + c] = NEG;
           }
-          const float4* st = reinterpret_cast<const float4*>(aux) + 4 * qd;
-          float lv[16], dvv[16];
-#pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) {
-            const float4 l4 = st[c4], d4 = st[16 + c4];
-            lv[4 * c4] = l4.x; lv[4 * c4 + 1] = l4.y; lv[4 * c4 + 2] = l4.z; lv[4 * c4 + 3] = l4.w;
-            dvv[4 * c4] = d4.x; dvv[4 * c4 + 1] = d4.y; dvv[4 * c4 + 2] = d4.z; dvv[4 * c4 + 3] = d4.w;
-          }
+          // the accumulators already hold S - LSE/scale and dP - rowsum(O dO) (statistics k-step)
           float pe[16], de[16];
 #pragma unroll
-          for (int c = 0; c < 16; ++c) pe[c] = fmaf(__uint_as_float(sr[hc][c0 + c]), scale_log2, -lv[c]);
+          for (int c = 0; c < 16; ++c) pe[c] = fast_exp2(__uint_as_float(sr[hc][c0 + c]) * scale_log2);
 #pragma unroll
-          for (int c = 0; c < 16; ++c) pe[c] = fast_exp2(pe[c]);
-#pragma unroll
-          for (int c = 0; c < 16; ++c) de[c] = __uint_as_float(dr[hc][c0 + c]) - dvv[c];
-#pragma unroll
-          for (int c = 0; c < 16; ++c) de[c] *= pe[c];
+          for (int c = 0; c < 16; ++c) de[c] = pe[c] * __uint_as_float(dr[hc][c0 + c]);
           uint32_t pk1[8], pk2[8];
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
@@ -509,17 +509,16 @@ bwd_sm100_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
         if (elect_one()) {
           const uint32_t dst = sRing + slot * Cfg::SLOT_BYTES;
           const uint32_t fb = bar(Cfg::B_RFULL + slot);
-          mbar_arrive_expect_tx(fb, Cfg::SLOT_BYTES * D / 128);
+          mbar_arrive_expect_tx(fb, Cfg::SLOT_BYTES * D / 128 + Cfg::AUX_BYTES);
           for (int dc = 0; dc < D / 64; ++dc) {
             tma_load_4d(dst + dc * Cfg::SUB64, &tm_q, fb, dc * 64, hstr, idx * 64, b);
             tma_load_4d(dst + Cfg::HALF_BYTES + dc * Cfg::SUB64, &tm_do, fb, dc * 64, hstr, idx * 64, b);
           }
-          const int64_t at = ((int64_t)b * p.Hq + hstr) * p.Sq_r + idx * 64;
-          const uint32_t ax = sbase + Cfg::OFF_AUX + (kk % Cfg::NAUX) * Cfg::AUX_BYTES;
-          const uint32_t ab = bar(Cfg::B_AFULL + kk % Cfg::NAUX);
-          mbar_arrive_expect_tx(ab, 512);
-          fbulk_copy_g2s(ax, p.lse_log2 + at, 256, ab);
-          fbulk_copy_g2s(ax + 256, p.dpsum + at, 256, ab);
+          // statistics operands of the 64 queries: 16 bytes per query and array, contiguous in global memory
+          const int64_t at = (((int64_t)b * p.Hq + hstr) * p.Sq_r + idx * 64) * 8;
+          const uint32_t ax = sbase + Cfg::OFF_AUX + slot * Cfg::AUX_BYTES;
+          fbulk_copy_g2s(ax, p.stat_s + at, 1024, fb);
+          fbulk_copy_g2s(ax + 1024, p.stat_dp + at, 1024, fb);
         }
       }
       if (!ok) break;
@@ -536,6 +535,8 @@ bwd_sm100_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
       const uint64_t dKk = make_sdesc(sStat, 16, 1024);                     // K tile, K-major (A of S^T)
       const uint64_t dVk = make_sdesc(sStat + Cfg::TILE_BYTES, 16, 1024);   // V tile, K-major (A of dP^T)
       const uint64_t dRk = make_sdesc(sRing, 16, 1024);                     // K-major view of a ring slot
+      // 128 rows of ones: 8-row groups 128 bytes apart; the second core matrix of a group is the next group
+      const uint64_t dOnes = make_sdesc_noswz(sbase + Cfg::OFF_ONES, 128, 128);
       bool ok = true;
       int kb = 0;
       for (int j = 0; ok; ++j) {
@@ -562,12 +563,21 @@ bwd_sm100_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
           tc_fence_after();
           const uint64_t dq_ = dRk + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));
           const uint64_t do_ = dq_ + (uint64_t)(Cfg::HALF_BYTES >> 4);
+          // statistics operands of this slot: B rows 16 bytes apart (8-row groups 128 bytes apart), its second
+          // core matrix is the block of zeros further up in shared memory
+          const uint32_t sAux = sbase + Cfg::OFF_AUX + slot * Cfg::AUX_BYTES;
+          const uint64_t dSs = make_sdesc_noswz(sAux, sbase + Cfg::OFF_ZEROS - sAux, 128);
+          const uint64_t dSd = make_sdesc_noswz(sAux + 1024, sbase + Cfg::OFF_ZEROS - (sAux + 1024), 128);
           if constexpr (D == 128) {
             umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(tmem + C_S, dKk, dq_, idesc_g, 0u);
+            umma_ss(tmem + C_S, dOnes, dSs, idesc_g, 1u);
             umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(tmem + C_DP, dVk, do_, idesc_g, 0u);
+            umma_ss(tmem + C_DP, dOnes, dSd, idesc_g, 1u);
           } else {
             umma_ss_x4(tmem + C_S, dKk, dq_, idesc_g, 0u);
+            umma_ss(tmem + C_S, dOnes, dSs, idesc_g, 1u);
             umma_ss_x4(tmem + C_DP, dVk, do_, idesc_g, 0u);
+            umma_ss(tmem + C_DP, dOnes, dSd, idesc_g, 1u);
           }
           tc_commit(bar(Cfg::B_GFULL + pz));
           if (k == K_items - 1) tc_commit(bar(Cfg::B_VFREE));   // that was the unit's last read of V
@@ -826,7 +836,7 @@ static int launch_bwd_sm100_fused(const AttnKParams& p, const fm_attn_args* a, c
   }
   auto kern = bwd_sm100_fused_kernel<IS_BF16, D>;
   FM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
-  FM_CUDA_TRY(cudaMemsetAsync(p.dq_accum, 0, bwd_sm100_fused_accum_bytes(a), s));
+  if (!(p.bwd_flags & FM_BWD_DQ_CARRY)) FM_CUDA_TRY(cudaMemsetAsync(p.dq_accum, 0, bwd_sm100_fused_accum_bytes(a), s));
   int dev = 0, n_sm = 0;
   FM_CUDA_TRY(cudaGetDevice(&dev));
   FM_CUDA_TRY(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
@@ -836,9 +846,12 @@ static int launch_bwd_sm100_fused(const AttnKParams& p, const fm_attn_args* a, c
   FM_CUDA_TRY(cudaGetLastError());
   const int64_t n = (int64_t)p.B * p.Hq * p.Sq * (D / 8);
   const unsigned blocks = (unsigned)std::min<int64_t>((n + 255) / 256, (int64_t)n_sm * 16);
-  bwd_dq_round_kernel<IS_BF16, D><<<blocks, 256, 0, s>>>(p);
-  FM_CUDA_TRY(cudaGetLastError());
-  count_launches(2);
+  if (!(p.bwd_flags & FM_BWD_DQ_LEAVE)) {
+    bwd_dq_round_kernel<IS_BF16, D><<<blocks, 256, 0, s>>>(p);
+    FM_CUDA_TRY(cudaGetLastError());
+    count_launches(1);
+  }
+  count_launches(1);
   return FM_OK;
 }
 

@@ -144,6 +144,47 @@ __global__ void __launch_bounds__(256) cp_merge_kernel(float* __restrict__ acc, 
   if (lane == 0) lse_run[li] = ln;
 }
 
+// Merge of exactly two forward partials straight into the 16-bit output:
+//   lse = logaddexp(lse_a, lse_b); out = o_a*exp(lse_a-lse) + o_b*exp(lse_b-lse), rounded once.
+// One warp per (b, s, h) row; reads two 16-bit rows, writes one (no fp32 accumulator round trip).
+template <bool IS_BF16>
+__global__ void __launch_bounds__(256) cp_merge_two_kernel(const uint16_t* o_a, const float* __restrict__ lse_a,
+                                                          const uint16_t* __restrict__ o_b, const float* __restrict__ lse_b,
+                                                          uint16_t* out, float* __restrict__ lse_out,
+                                                          int B, int S, int H, int dv) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + warp;  // (b, s, h)
+  if (row >= (int64_t)B * S * H) return;
+  const int h = (int)(row % H);
+  const int64_t bs = row / H;
+  const int s = (int)(bs % S);
+  const int b = (int)(bs / S);
+  const int64_t li = ((int64_t)b * H + h) * S + s;
+  const float la = lse_a[li], lb = lse_b[li];
+  const float mx = fmaxf(la, lb);
+  float wa = 0.f, wb = 0.f, ln = -INFINITY;
+  if (mx != -INFINITY) {
+    const float ea = __expf(la - mx), eb = __expf(lb - mx);
+    ln = mx + __logf(ea + eb);
+    wa = __expf(la - ln); wb = __expf(lb - ln);
+  }
+  const uint16_t* pa = o_a + row * dv;
+  const uint16_t* pb = o_b + row * dv;
+  uint16_t* po = out + row * dv;
+  for (int c = lane * 8; c < dv; c += 256) {
+    const uint4 ra = *reinterpret_cast<const uint4*>(pa + c), rb = *reinterpret_cast<const uint4*>(pb + c);
+    const uint32_t av[4] = {ra.x, ra.y, ra.z, ra.w}, bv[4] = {rb.x, rb.y, rb.z, rb.w};
+    uint32_t ov[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 x = unpack2<IS_BF16>(av[e]), y = unpack2<IS_BF16>(bv[e]);
+      ov[e] = pack2<IS_BF16>(x.x * wa + y.x * wb, x.y * wa + y.y * wb);
+    }
+    *reinterpret_cast<uint4*>(po + c) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+  }
+  if (lane == 0) lse_out[li] = ln;
+}
+
 template <bool IS_BF16>
 __global__ void cp_add_kernel(float* __restrict__ acc, const uint16_t* __restrict__ x, int64_t n, int first) {
   const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
@@ -246,6 +287,23 @@ extern "C" int fm_cp_merge_partial(float* acc, float* lse_run, const void* o_s, 
     cp_merge_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(acc, lse_run, (const uint16_t*)o_s, lse_s, B, S, H, dv, first);
   else
     cp_merge_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(acc, lse_run, (const uint16_t*)o_s, lse_s, B, S, H, dv, first);
+  count_launches(1);
+  FM_CUDA_TRY(cudaGetLastError());
+  return FM_OK;
+}
+
+extern "C" int fm_cp_merge_two(const void* o_a, const float* lse_a, const void* o_b, const float* lse_b, void* out,
+                               float* lse_out, int B, int S, int H, int dv, int dtype, void* stream) {
+  FM_REQUIRE(o_a && lse_a && o_b && lse_b && out && lse_out && dv % 8 == 0, FM_ERR_INVALID_ARGUMENT,
+             "fm_cp_merge_two: bad arguments (dv must be a multiple of 8)");
+  const int64_t rows = (int64_t)B * S * H;
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  if (dtype == FM_DTYPE_BF16)
+    cp_merge_two_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)o_a, lse_a, (const uint16_t*)o_b, lse_b,
+                                                                      (uint16_t*)out, lse_out, B, S, H, dv);
+  else
+    cp_merge_two_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)o_a, lse_a, (const uint16_t*)o_b, lse_b,
+                                                                       (uint16_t*)out, lse_out, B, S, H, dv);
   count_launches(1);
   FM_CUDA_TRY(cudaGetLastError());
   return FM_OK;

@@ -255,8 +255,14 @@ def _flash_attn_fwd(q, k, v, startend_row_indices=None, softmax_scale=None, caus
 
 def _flash_attn_bwd(q, k, v, out, dout, lse, startend_row_indices=None, softmax_scale=None,
                     causal=False, learnable_sink=None, deterministic=False,
-                    mask_info: Optional[FlashMaskInfo] = None):
+                    mask_info: Optional[FlashMaskInfo] = None, dq_chain: Optional[dict] = None):
     """Backward.  Returns (dq, dk, dv, dsink | None).
+
+    ``dq_chain`` (context parallel): a dict shared by the backward calls over the same queries
+    (``{"last": bool}`` set by the caller for each call).  When the one-kernel backward serves
+    the calls, their dQ is summed in its fp32 accumulator and rounded once: every call but the
+    last returns ``dq = None``.  When another variant serves them, every call returns its own dq
+    and the caller adds them; ``dq_chain["summed"]`` tells which happened.
 
     Reference: _flash_attn_bwd, flashmask/cute/ops/bwd.py:56-1261."""
     idx = startend_row_indices
@@ -288,9 +294,25 @@ def _flash_attn_bwd(q, k, v, out, dout, lse, startend_row_indices=None, softmax_
         a.dq_order = _launch_order(a, info, _lib.FM_ORDER_BWD_DQ, q)
         a.dkdv_order = _launch_order(a, info, _lib.FM_ORDER_BWD_DKDV, q)
     nbytes = lib.fm_bwd_workspace_bytes(C.byref(a))
-    ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=q.device)
+    chained = dq_chain is not None and bool(lib.fm_bwd_accumulates(C.byref(a)))
+    if chained:
+        # one workspace for the whole chain: the accumulator carries the sums from call to call
+        if "ws" in dq_chain:
+            a.bwd_flags |= _lib.FM_BWD_DQ_CARRY
+        else:
+            dq_chain["ws"] = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=q.device)
+        if not dq_chain.get("last", False):
+            a.bwd_flags |= _lib.FM_BWD_DQ_LEAVE
+        ws = dq_chain["ws"]
+        assert ws.numel() >= nbytes, "the backward calls of a chain must share one problem geometry"
+    else:
+        ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=q.device)
+    if dq_chain is not None:
+        dq_chain["summed"] = chained
     a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
     _lib.check(lib.fm_bwd(C.byref(a), _stream(q)), "fm_bwd")
+    if chained and not dq_chain.get("last", False):
+        dq = None
     if _kv_shared(k, v):
         # value is a view of key's leading dv columns on the same storage: the
         # gradient of that storage is dK with dV folded into its leading columns,

@@ -103,6 +103,17 @@ FM_API int fm_mask_prepare(const int32_t* mask, int B, int Hm, int Sq, int Sk, i
 FM_API int fm_mask_count_visible(const int32_t* mask, int B, int Hm, int Sq, int Sk,
                           int ncols, int causal, int64_t* out, void* stream);
 
+/* dQ of several backward calls over the same queries (context parallel: own
+ * shard, pulled shards) can be summed inside the fp32 accumulator of the
+ * one-kernel backward instead of being rounded per call and added afterwards:
+ * the first call sets FM_BWD_DQ_LEAVE (dq is not written, the accumulator keeps
+ * the sums), later calls pass the SAME workspace and set FM_BWD_DQ_CARRY (the
+ * accumulator is not cleared), the last one leaves FM_BWD_DQ_LEAVE off and
+ * writes dq once.  Ignored by the other backward variants; fm_bwd_accumulates()
+ * says whether the variant a call would take honours them. */
+#define FM_BWD_DQ_CARRY 1
+#define FM_BWD_DQ_LEAVE 2
+
 /* Arguments shared by forward and backward.  Strides are in ELEMENTS; the
  * innermost (head-dim) stride is 1.  Layouts follow the reference:
  * q/o/do/dq [B,Sq,Hq,*], k/dk [B,Sk,Hkv,d], v/dv [B,Sk,Hkv,dv],
@@ -121,7 +132,8 @@ typedef struct fm_attn_args {
                              backward may be used (d = dv = 64 or 128), whose dQ
                              is summed by reductions in an order that is not
                              fixed                                            */
-  int32_t reserved0;
+  int32_t bwd_flags;      /* backward only, one-kernel variant: FM_BWD_* bits below, 0 = a
+                             self-contained call                               */
   float softmax_scale;
   float reserved1;
   const void* q; const void* k; const void* v;
@@ -269,6 +281,9 @@ FM_API int fm_selftest_bounded_wait(int budget_us, void* stream);
  * postprocess, flash_bwd_postprocess.py).  Ask for the size with the same
  * args->deterministic the call will carry. */
 FM_API size_t fm_bwd_workspace_bytes(const fm_attn_args* args);
+/* 1 when fm_bwd(args) would run the one-kernel variant (and so honours
+ * args->bwd_flags), else 0. */
+FM_API int fm_bwd_accumulates(const fm_attn_args* args);
 FM_API int fm_bwd(const fm_attn_args* args, void* stream);
 
 /* ------------------------------------------------------------------------
@@ -329,6 +344,11 @@ FM_API int fm_cp_shard_visible(const int32_t* mask, int B, int Hm, int Sq, int S
  * (tests/torch/distributed/all_gather_flashmask.py:29-111). */
 FM_API int fm_cp_merge_partial(float* acc, float* lse_run, const void* o_s, const float* lse_s, int B, int S,
                                int H, int dv, int dtype, int first, void* stream);
+/* The same merge for exactly two partials, written straight to the 16-bit output
+ * (out [B,S,H,dv], lse_out [B,H,S]) with one rounding: what the context-parallel
+ * forward needs (own shard + pulled shards).  May run in place (out == o_a). */
+FM_API int fm_cp_merge_two(const void* o_a, const float* lse_a, const void* o_b, const float* lse_b, void* out,
+                           float* lse_out, int B, int S, int H, int dv, int dtype, void* stream);
 FM_API int fm_cp_accumulate(float* acc, const void* x, int64_t n, int dtype, int first, void* stream);
 FM_API int fm_cp_cast(const float* acc, void* out, int64_t n, int dtype, void* stream);
 
