@@ -214,10 +214,12 @@ def run_cp(args, rank, local_rank, world):
     barrier()
     sampler.mark()
     n0 = _lib.load().fm_launch_count()
+    t_host = time.perf_counter()
     e0.record()
     for i in range(args.steps):
         step(*ins[i])
     e1.record()
+    host_ms = (time.perf_counter() - t_host) * 1e3 / args.steps     # host time to ENQUEUE a step
     launches = torch.tensor([_lib.load().fm_launch_count() - n0], device=dev, dtype=torch.int64)
     barrier()
     clocks = sampler.stop()
@@ -281,7 +283,7 @@ def run_cp(args, rank, local_rank, world):
                        "l2": "per-rank tensors exceed the 126 MB L2; no flush between steps",
                        "mask_sparsity": round(w.sparsity(), 4), "parallelism": f"cp{world}",
                        "partition_ms": partition_ms, "rank_loads": loads},
-            "clocks": clocks, "e2e": e2e, "cp_parity": parity,
+            "clocks": clocks, "e2e": e2e, "cp_parity": parity, "host_enqueue_ms_per_step": round(host_ms, 3),
             "gpu_launches": int(launches.item()), "tokens_per_s": w.B * w.Sq / (ms_step * 1e-3),
             "roofline": {"bound": "tensor", "kernel": "fwd + bwd tcgen05 kernels over all ring steps (aggregate)",
                          "achieved": value / world, "peak": peak_tf, "unit": "TFLOP/s",

@@ -72,9 +72,10 @@ def phase_report() -> Dict[str, float]:
         return out
     torch.cuda.synchronize()
     for (n0, e0), (n1, e1) in zip(_PHASES[:-1], _PHASES[1:]):
-        if n1.endswith(":begin"):
-            continue
-        out[n1] = out.get(n1, 0.0) + e0.elapsed_time(e1)
+        # the stretch that ends at a ":begin" mark is what lies between two calls (host work, other
+        # kernels of the step): reported as "gap_before_fwd" / "gap_before_bwd"
+        name = "gap_before_" + n1[:-6] if n1.endswith(":begin") else n1
+        out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
     _PHASES = []
     return out
 

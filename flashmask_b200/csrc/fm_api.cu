@@ -73,7 +73,8 @@ int option_order_classes() { return g_opt.order_classes; }
 // Kernel variant of the forward for (d, dv): the tcgen05 kernels cover head dims up to
 // 128 (multiples of 8); FLASHMASK_B200_FWD=mma forces the warp-MMA variant (A/B runs).
 static bool fwd_uses_sm100(int d, int dv) {
-  if (d > 128 || dv > 128 || d % 8 || dv % 8) return false;
+  const bool small = d <= 128 && dv <= 128 && d % 8 == 0 && dv % 8 == 0;
+  if (!small && !(d == 192 && dv == 128)) return false;
   return !g_opt.fwd_mma;
 }
 
@@ -236,8 +237,8 @@ static int fwd_impl(const fm_attn_args* a, const BlockScore& bs, void* stream) {
     p.block_log2 = bs.block_size == 32 ? 5 : (bs.block_size == 64 ? 6 : 7);
     // the tcgen05 kernels have compile-time variants for it; the warp-MMA kernels (head dims above 128,
     // or FLASHMASK_B200_FWD=mma) a run-time branch
-    if (fwd_uses_sm100(a->d, a->dv) && fwd_sm100_supported(a)) return fwd_sm100_launch(p, a, (cudaStream_t)stream);
-    FM_REQUIRE(!fwd_uses_sm100(a->d, a->dv), FM_ERR_INVALID_ARGUMENT, "fm_fwd_block_score: q/k/v must be 16-byte aligned");
+    if (a->d <= 128 && fwd_uses_sm100(a->d, a->dv) && fwd_sm100_supported(a)) return fwd_sm100_launch(p, a, (cudaStream_t)stream);
+    FM_REQUIRE(a->d > 128 || !fwd_uses_sm100(a->d, a->dv), FM_ERR_INVALID_ARGUMENT, "fm_fwd_block_score: q/k/v must be 16-byte aligned");
     return fwd_mma_launch(p, a->dtype, (cudaStream_t)stream);
   }
   if (fwd_uses_sm100(a->d, a->dv) && fwd_sm100_supported(a)) return fwd_sm100_launch(p, a, (cudaStream_t)stream);

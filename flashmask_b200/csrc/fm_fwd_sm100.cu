@@ -40,14 +40,17 @@ __device__ long long g_fprof[64 * 8];
 #define FPROF_VAL(slot, v)
 #endif
 
-template <int D>
+// D: width q / k are computed at (64, 128 or 192), DV: width of v / o (64 or 128).
+template <int D, int DV = D>
 struct FwdSm100Cfg {
-  // the 64-column variant doubles the ring depth: its slots are half as large
-  static constexpr int BM = 128, BN = 128, NSTAGE = (D == 64 ? 8 : 4), NBND = 2, LIST_MAX = 2048;
+  // the 64-column variant doubles the ring depth: its slots are half as large; the 192-column one has room
+  // for two slots (one K tile and one V tile in flight) beside its two 48 KB Q sub-tiles
+  static constexpr int BM = 128, BN = 128, NSTAGE = (D == 64 ? 8 : (D > 128 ? 2 : 4)), NBND = 2, LIST_MAX = 2048;
   static constexpr int NTHREADS = 384;
   static constexpr int SUB = 128 * 128;                 // bytes of a 128-row x 64-col bf16 sub-tile
   static constexpr int Q_BYTES = BM * D * 2;
-  static constexpr int SLOT_BYTES = BN * D * 2;
+  static constexpr int K_BYTES = BN * D * 2, V_BYTES = BN * DV * 2;
+  static constexpr int SLOT_BYTES = K_BYTES > V_BYTES ? K_BYTES : V_BYTES;
   static constexpr int BND_BYTES = 128 * 4 * 4;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_KV = OFF_Q + 2 * Q_BYTES;
@@ -64,7 +67,8 @@ struct FwdSm100Cfg {
   static constexpr int B_QFULL = 0, B_KVFULL = 2, B_KVEMPTY = 2 + NSTAGE, B_SFULL = 2 + 2 * NSTAGE,
                        B_PFULL = B_SFULL + 2, B_ODONE = B_PFULL + 2, B_BNDFULL = B_ODONE + 2,
                        B_BNDEMPTY = B_BNDFULL + NBND, B_COUNT = B_BNDEMPTY + NBND;
-  static_assert(D == 64 || D == 128, "head-dim variants");
+  static_assert((D == 64 && DV == 64) || (D == 128 && DV == 128) || (D == 192 && DV == 128), "head-dim variants");
+  static_assert(SMEM_BS <= 227 * 1024 && SMEM <= 227 * 1024, "shared memory");
   static_assert(B_COUNT <= 32, "barrier storage");
   static_assert(NSTAGE * SLOT_BYTES >= LIST_MAX * 8 * 4, "the ring stages the reductions of the list build");
   static_assert(SMEM > 120 * 1024, "one CTA per SM is assumed by the 512-column TMEM allocation");
@@ -74,12 +78,11 @@ __device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); 
 
 // BLOCK_SCORE: 0, or the block size (32 / 64 / 128) of the block-score side output; BLOCK_BOS: document
 // starts are given, so a block may straddle two tiles.
-template <int D, bool IS_BF16, int BLOCK_SCORE, bool BLOCK_BOS>
+template <int D, int DV, bool IS_BF16, int BLOCK_SCORE, bool BLOCK_BOS>
 __global__ void __launch_bounds__(384, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const AttnKParams p) {
-  using Cfg = FwdSm100Cfg<D>;
-  constexpr int DV = D;
+  using Cfg = FwdSm100Cfg<D, DV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
@@ -363,8 +366,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             const uint32_t par = ((uint32_t)(k / Cfg::NSTAGE) & 1u) ^ 1u;
             ok = mbar_wait(bar(Cfg::B_KVEMPTY + slot), par, wc);
             if (!ok) break;
-            mbar_arrive_expect_tx(bar(Cfg::B_KVFULL + slot), Cfg::SLOT_BYTES);
-            for (int dc = 0; dc < D / 64; ++dc)
+            mbar_arrive_expect_tx(bar(Cfg::B_KVFULL + slot), kv == 0 ? Cfg::K_BYTES : Cfg::V_BYTES);
+            for (int dc = 0; dc < (kv == 0 ? D : DV) / 64; ++dc)
               tma_load_4d(sKV + slot * Cfg::SLOT_BYTES + dc * Cfg::SUB, kv == 0 ? &tm_k : &tm_v,
                           bar(Cfg::B_KVFULL + slot), dc * 64, hk, j0, b);
           }
@@ -409,7 +412,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           const uint64_t db = dk0 + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));
           const uint32_t dst = tmem + 128u * s;
           if constexpr (D == 128) umma_ss_x8<(Cfg::SUB >> 4), (Cfg::SUB >> 4)>(dst, da, db, idesc_qk, 0u);
-          else umma_ss_x4(dst, da, db, idesc_qk, 0u);
+          else if constexpr (D == 192) {
+            // three 64-column sub-tiles of q / k: eight k-steps, then four more on top
+            umma_ss_x8<(Cfg::SUB >> 4), (Cfg::SUB >> 4)>(dst, da, db, idesc_qk, 0u);
+            umma_ss_x4(dst, da + (uint64_t)(2 * (Cfg::SUB >> 4)), db + (uint64_t)(2 * (Cfg::SUB >> 4)), idesc_qk, 1u);
+          } else umma_ss_x4(dst, da, db, idesc_qk, 0u);
           tc_commit(bar(Cfg::B_SFULL + s));
         };
         auto issue_pv = [&](auto sub, int i) {
@@ -533,14 +540,15 @@ int bounded_wait_selftest_launch(uint64_t budget_ns, cudaStream_t s) {
 }
 
 bool fwd_sm100_supported(const fm_attn_args* a) {
-  if (a->d > 128 || a->dv > 128 || a->d % 8 || a->dv % 8) return false;
+  const bool small = a->d <= 128 && a->dv <= 128 && a->d % 8 == 0 && a->dv % 8 == 0;
+  if (!small && !(a->d == 192 && a->dv == 128)) return false;
   if (((uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v) & 15) return false;
   return true;
 }
 
-template <int D, bool IS_BF16, int BLOCK_SCORE, bool BLOCK_BOS>
+template <int D, int DV, bool IS_BF16, int BLOCK_SCORE, bool BLOCK_BOS>
 static int launch_fwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
-  using Cfg = FwdSm100Cfg<D>;
+  using Cfg = FwdSm100Cfg<D, DV>;
   FM_REQUIRE((a->Sk + 127) / 128 <= Cfg::LIST_MAX, FM_ERR_UNSUPPORTED,
              "forward: Sk=%d exceeds the %d keys this kernel variant indexes", a->Sk, Cfg::LIST_MAX * 128);
   CUtensorMap tq, tk, tv;
@@ -548,7 +556,7 @@ static int launch_fwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStr
   if ((rc = make_bshd_tmap(&tq, a->q, a->dtype, a->B, a->Sq, a->Hq, a->d, a->q_stride[0], a->q_stride[1], a->q_stride[2], 128))) return rc;
   if ((rc = make_bshd_tmap(&tk, a->k, a->dtype, a->B, a->Sk, a->Hkv, a->d, a->k_stride[0], a->k_stride[1], a->k_stride[2], 128))) return rc;
   if ((rc = make_bshd_tmap(&tv, a->v, a->dtype, a->B, a->Sk, a->Hkv, a->dv, a->v_stride[0], a->v_stride[1], a->v_stride[2], 128))) return rc;
-  auto kern = fwd_sm100_kernel<D, IS_BF16, BLOCK_SCORE, BLOCK_BOS>;
+  auto kern = fwd_sm100_kernel<D, DV, IS_BF16, BLOCK_SCORE, BLOCK_BOS>;
   constexpr int smem_bytes = BLOCK_BOS ? Cfg::SMEM_BS : Cfg::SMEM;
   FM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   dim3 grid((p.Sq + 255) / 256, p.Hq, p.B);
@@ -561,11 +569,16 @@ static int launch_fwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStr
 int fwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
   const bool bf = a->dtype == FM_DTYPE_BF16;
   const bool small = a->d <= 64 && a->dv <= 64;
+  if (a->d == 192) {
+    // 192 / 128: the plain forward only (the block-score side output of this head dim stays on the warp-MMA kernel)
+    FM_REQUIRE(!p.block_logit, FM_ERR_UNSUPPORTED, "forward: no block scores in the 192-column tcgen05 variant");
+    return bf ? launch_fwd_sm100<192, 128, true, 0, false>(p, a, s) : launch_fwd_sm100<192, 128, false, 0, false>(p, a, s);
+  }
 #define FM_FWD_DISPATCH(BSZ, BOS)                                                                         \
   do {                                                                                                    \
     if (small)                                                                                            \
-      return bf ? launch_fwd_sm100<64, true, BSZ, BOS>(p, a, s) : launch_fwd_sm100<64, false, BSZ, BOS>(p, a, s); \
-    return bf ? launch_fwd_sm100<128, true, BSZ, BOS>(p, a, s) : launch_fwd_sm100<128, false, BSZ, BOS>(p, a, s); \
+      return bf ? launch_fwd_sm100<64, 64, true, BSZ, BOS>(p, a, s) : launch_fwd_sm100<64, 64, false, BSZ, BOS>(p, a, s); \
+    return bf ? launch_fwd_sm100<128, 128, true, BSZ, BOS>(p, a, s) : launch_fwd_sm100<128, 128, false, BSZ, BOS>(p, a, s); \
   } while (0)
   if (p.block_logit && p.block_bos) {
     if (p.block_log2 == 5) FM_FWD_DISPATCH(32, true);

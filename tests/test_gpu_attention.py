@@ -132,6 +132,15 @@ def test_head_dims(kind, d, dv, Hq, Hkv):
 
 
 @pytest.mark.parametrize("kind", MASKS)
+def test_masks_d192(kind):
+    """Every mask family through the 192 / 128 forward variant of the tcgen05 kernel (two-slot K/V ring,
+    twelve k-steps per score GEMM): GQA, ragged sizes, rows long enough to wrap the ring many times."""
+    _run(kind, 2, 384, 384, 4, 2, 192, 128, seed=31)
+    _run(kind, 1, 1411, 1411, 2, 1, 192, 128, sink=True, seed=32)
+    assert _kernel_status() == 0
+
+
+@pytest.mark.parametrize("kind", MASKS)
 def test_masks_d64(kind, fwd_variant):
     """Every mask family through the 64-column variants: GQA, rows long enough to wrap the K/V ring."""
     _run(kind, 2, 384, 384, 4, 2, 64, 64, seed=21)
