@@ -186,6 +186,8 @@ static int run_bwd_kernels(const fm_attn_args* a, const AttnKParams& p, cudaStre
     // (documents, windows) and 3-5 % slower where every unit is hundreds of items long (its main loop
     // is slightly slower; the table records in [E+2] which side of that line a mask is on).
     // FLASHMASK_B200_PERSIST=0 keeps the one-unit-per-CTA variant.
+    // (Without tables the persistent kernels also work, one unit per CTA, bitwise the same; measured on dense
+    // masks they are 5-12 % slower than the one-unit kernels, which is why both exist.)
     const bool persist = p.dq_order && p.dkdv_order && g_opt.bwd_persist;
     rc = persist ? bwd_sm100_persist_launch(p, a, s) : bwd_sm100_launch(p, a, s);
   } else {
