@@ -421,6 +421,12 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const AttnKParams p
   }
 #pragma unroll
   for (int o2 = LPR / 2; o2; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
+  if (p.dq_accum && !(p.bwd_flags & FM_BWD_DQ_CARRY) && row < p.Sq_r) {
+    // one-kernel backward: this row of the fp32 dQ accumulator starts at zero (the lanes of the row share it)
+    const int dacc = (p.d <= 64 && p.dv_dim <= 64) ? 64 : 128;
+    float4* z = reinterpret_cast<float4*>(p.dq_accum + (((int64_t)b * p.Hq + hq) * p.Sq_r + row) * dacc);
+    for (int c = ln; c < dacc / 4; c += LPR) z[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   if (ln == 0 && row < p.Sq_r) {
     const int64_t at = ((int64_t)b * p.Hq + hq) * p.Sq_r + row;
     p.dpsum[at] = acc;

@@ -836,7 +836,7 @@ static int launch_bwd_sm100_fused(const AttnKParams& p, const fm_attn_args* a, c
   }
   auto kern = bwd_sm100_fused_kernel<IS_BF16, D>;
   FM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
-  if (!(p.bwd_flags & FM_BWD_DQ_CARRY)) FM_CUDA_TRY(cudaMemsetAsync(p.dq_accum, 0, bwd_sm100_fused_accum_bytes(a), s));
+  // (the accumulator was cleared by the preprocess kernel, row by row, unless this call carries earlier sums)
   int dev = 0, n_sm = 0;
   FM_CUDA_TRY(cudaGetDevice(&dev));
   FM_CUDA_TRY(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
