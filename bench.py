@@ -485,9 +485,9 @@ def main():
     peak_tf = peaks.get("bf16_tflops_sustained") or 1400.0
     peak_src = "measured (sustained cuBLAS bf16)" if peaks else "fallback"
     dom = "bwd" if ms_bwd >= ms_fwd else "fwd"
-    # DRAM bytes per launch of this workload from one ncu capture: forward kernel; backward = preprocess +
-    # 256 MB clear + one-kernel backward + dQ rounding (the two-kernel backward measured 1771 MB)
-    NCU_DRAM_BYTES = {"fwd": 389.2e6, "bwd": 3494.0e6 if not det else 1771.0e6}
+    # DRAM bytes per launch of this workload from one ncu capture: forward kernel; backward = preprocess (with
+    # the accumulator clear) + one-kernel backward + dQ rounding (the two-kernel backward measured 1771 MB)
+    NCU_DRAM_BYTES = {"fwd": 389.9e6, "bwd": 3495.0e6 if not det else 1771.0e6}
     dom_flops, dom_ms = (bwd_flops, ms_bwd) if dom == "bwd" else (fwd_flops, ms_fwd)
     ach = dom_flops / (dom_ms * 1e-3) / 1e12
     bwd_kind = ("preprocess + dK/dV + dQ kernels" if det or w.d != w.dv or w.d not in (64, 128) else
