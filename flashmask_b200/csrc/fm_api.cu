@@ -155,7 +155,8 @@ extern "C" int fm_reload_options(void) {
 }
 
 static bool bwd_uses_sm100(int d, int dv) {
-  if (d > 128 || dv > 128 || d % 8 || dv % 8) return false;
+  const bool small = d <= 128 && dv <= 128 && d % 8 == 0 && dv % 8 == 0;
+  if (!small && !(d == 192 && dv == 128)) return false;
   return !g_opt.bwd_mma;
 }
 
@@ -188,7 +189,7 @@ static int run_bwd_kernels(const fm_attn_args* a, const AttnKParams& p, cudaStre
     // FLASHMASK_B200_PERSIST=0 keeps the one-unit-per-CTA variant.
     // (Without tables the persistent kernels also work, one unit per CTA, bitwise the same; measured on dense
     // masks they are 5-12 % slower than the one-unit kernels, which is why both exist.)
-    const bool persist = p.dq_order && p.dkdv_order && g_opt.bwd_persist;
+    const bool persist = p.dq_order && p.dkdv_order && g_opt.bwd_persist && a->d <= 128;   // 192 / 128: one-unit kernels only
     rc = persist ? bwd_sm100_persist_launch(p, a, s) : bwd_sm100_launch(p, a, s);
   } else {
     rc = bwd_mma_launch(p, a->dtype, s);

@@ -1,7 +1,8 @@
 // Backward attention on the 5th-generation tensor cores (tcgen05 / UMMA) for
 // head dims up to 128 (smaller ones, multiples of 8, are computed at width 128:
 // the TMA loads fill the columns past the end of a head with zeros and the
-// epilogues leave them unwritten), as two kernels that share one pipeline skeleton:
+// epilogues leave them unwritten) and for d = 192 / dv = 128, as two kernels that
+// share one pipeline skeleton:
 //
 //   MODE_DKDV  one CTA per (128-key tile, kv head, batch).  K and V stay in
 //              shared memory; 64-row halves of Q and dO stream through a ring
@@ -56,16 +57,24 @@ __device__ long long g_prof[2 * 64 * 16];   // [mode][cta][stamp]
 #define PROF_VAL(slot, v)
 #endif
 
+// D: width the d-wide operands (Q, K, dQ, dK) are computed at.  Up to 128 the layout is the one of
+// D = 128 (a 64-column variant leaves the second sub-tile of every operand unloaded); D = 192 has
+// three 64-column sub-tiles per d-wide operand and a three-slot ring.  The dv-wide operands (V, dO,
+// dV) always have room for 128 columns.
+template <int D>
 struct BwdSm100Cfg {
-  static constexpr int NSLOT = 4, LIST_MAX = 2048, NTHREADS = 384;
-  static constexpr int TILE_BYTES = 128 * 128 * 2;     // 128 rows x 128 cols bf16
+  static constexpr int W1 = D > 128 ? D : 128;
+  static constexpr int NSLOT = D > 128 ? 3 : 4, LIST_MAX = 2048, NTHREADS = 384;
   static constexpr int SUB128 = 128 * 128;             // 128-row x 64-col sub-tile (bytes)
   static constexpr int SUB64 = 64 * 128;               // 64-row x 64-col sub-tile (bytes)
-  static constexpr int HALF_BYTES = 2 * SUB64;         // one operand of a half tile
-  static constexpr int SLOT_BYTES = 2 * HALF_BYTES;    // both operands
+  static constexpr int STAT1_BYTES = 128 * W1 * 2;     // stationary K (dK/dV kernel) or Q (dQ kernel) tile
+  static constexpr int STAT2_BYTES = 128 * 128 * 2;    // stationary V or dO tile
+  static constexpr int OP1_BYTES = 64 * W1 * 2;        // streamed Q or K half tile
+  static constexpr int OP2_BYTES = 64 * 128 * 2;       // streamed dO or V half tile
+  static constexpr int SLOT_BYTES = OP1_BYTES + OP2_BYTES;
   static constexpr int AUX_BYTES = 1024;
   static constexpr int OFF_STAT = 0;
-  static constexpr int OFF_RING = OFF_STAT + 2 * TILE_BYTES;
+  static constexpr int OFF_RING = OFF_STAT + STAT1_BYTES + STAT2_BYTES;
   static constexpr int OFF_AUX = OFF_RING + NSLOT * SLOT_BYTES;
   static constexpr int OFF_LIST = OFF_AUX + NSLOT * AUX_BYTES;
   static constexpr int OFF_BAR = OFF_LIST + LIST_MAX * 4;
@@ -77,6 +86,15 @@ struct BwdSm100Cfg {
   static_assert(SMEM > 120 * 1024 && SMEM <= 227 * 1024, "one CTA per SM (512 TMEM columns)");
 };
 
+// Byte offset of 16-byte chunk `chunk` inside row `r` of an epilogue staging tile: the chunk index is
+// XOR-ed with the row so that the lanes of a warp (one row each, same chunk) hit different banks.  Rows of
+// 24 chunks (D = 192) swizzle inside groups of eight chunks, rows of 16 chunks over the whole row.
+template <bool BIG>
+__device__ __forceinline__ int stage_chunk(int chunk, int r) {
+  if constexpr (BIG) return ((chunk & ~7) | ((chunk ^ r) & 7)) << 4;
+  else return (chunk ^ (r & 15)) << 4;
+}
+
 __device__ __forceinline__ float bneg_inf() { return __int_as_float(0xff800000); }
 
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -85,15 +103,25 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
                : "memory");
 }
 
-// D: width the head dims are computed at (64 when both fit, else 128).  The 64-column variant
-// keeps the shared-memory layout of the 128-column one and simply leaves the second 64-column
-// sub-tile of every operand unloaded and unread: half the copies, half the tensor work.
-template <int MODE, bool IS_BF16, int D>
+// D / DV: widths the head dims are computed at: (64, 64) when both fit, (128, 128) up to 128, and
+// (192, 128).  The 64-column variant keeps the shared-memory layout of the 128-column one and simply
+// leaves the second 64-column sub-tile of every operand unloaded and unread: half the copies, half
+// the tensor work.
+//
+// At D = 192 the accumulators need 320 (dK 192 + dV 128) of the 512 tensor-memory columns, which
+// leaves three 64-column score buffers instead of four: S^T (S) keeps one buffer per item parity, dP^T
+// (dP) has a single buffer, and the bf16 operands P^T / dS^T (dS) of an item are written over the
+// S^T buffer of that item, which is dead once its warpgroup holds the scores in registers.  The
+// issue order then is: accumulation MMAs of item k, S^T of item k+2 (after them in the pipe, so
+// the overlay is no longer read), dP^T of item k+2 as soon as the other warpgroup has read dP^T of
+// item k+1 out of the single buffer.
+template <int MODE, bool IS_BF16, int D, int DV>
 __global__ void __launch_bounds__(384, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_constant__ CUtensorMap tm_stat2,
                  const __grid_constant__ CUtensorMap tm_str1, const __grid_constant__ CUtensorMap tm_str2,
                  const AttnKParams p) {
-  using Cfg = BwdSm100Cfg;
+  using Cfg = BwdSm100Cfg<D>;
+  constexpr bool BIG = D > 128;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
@@ -140,13 +168,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
     mbar_init(bar(Cfg::B_ACC), 1);
     fence_mbar_init();
     // the stationary tiles are requested right away: the loads overlap with the list build
-    mbar_arrive_expect_tx(bar(Cfg::B_STAT), 2 * Cfg::TILE_BYTES * D / 128);
+    mbar_arrive_expect_tx(bar(Cfg::B_STAT), (D / 64 + DV / 64) * Cfg::SUB128);
     {
       const int hs = (MODE == MODE_DKDV) ? hk : hq0;
-      for (int dc = 0; dc < D / 64; ++dc) {
+      for (int dc = 0; dc < D / 64; ++dc)
         tma_load_4d(sStat + dc * Cfg::SUB128, &tm_stat1, bar(Cfg::B_STAT), dc * 64, hs, row0, b);
-        tma_load_4d(sStat + Cfg::TILE_BYTES + dc * Cfg::SUB128, &tm_stat2, bar(Cfg::B_STAT), dc * 64, hs, row0, b);
-      }
+      for (int dc = 0; dc < DV / 64; ++dc)
+        tma_load_4d(sStat + Cfg::STAT1_BYTES + dc * Cfg::SUB128, &tm_stat2, bar(Cfg::B_STAT), dc * 64, hs, row0, b);
     }
     PROF(11);
   }
@@ -215,8 +243,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
     if (MODE == MODE_DKDV) {
       uint16_t* gk = reinterpret_cast<uint16_t*>(p.dk) + b * p.dk_b + (int64_t)row0 * p.dk_s + hk * p.dk_h;
       uint16_t* gv = reinterpret_cast<uint16_t*>(p.dv) + b * p.dv_b + (int64_t)row0 * p.dv_s + hk * p.dv_h;
-      for (int x = tid; x < 128 * 16; x += Cfg::NTHREADS) {
-        const int rr = x >> 4, cc = x & 15;
+      for (int x = tid; x < 128 * (Cfg::W1 / 8); x += Cfg::NTHREADS) {
+        const int rr = x / (Cfg::W1 / 8), cc = x % (Cfg::W1 / 8);
         if (row0 + rr < p.Sk) {
           if (cc * 8 < p.d) *reinterpret_cast<uint4*>(gk + (int64_t)rr * p.dk_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
           if (cc * 8 < p.dv_dim) *reinterpret_cast<uint4*>(gv + (int64_t)rr * p.dv_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
@@ -224,8 +252,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
       }
     } else {
       uint16_t* gq = reinterpret_cast<uint16_t*>(p.dq) + b * p.dq_b + (int64_t)row0 * p.dq_s + hq0 * p.dq_h;
-      for (int x = tid; x < 128 * 16; x += Cfg::NTHREADS) {
-        const int rr = x >> 4, cc = x & 15;
+      for (int x = tid; x < 128 * (Cfg::W1 / 8); x += Cfg::NTHREADS) {
+        const int rr = x / (Cfg::W1 / 8), cc = x % (Cfg::W1 / 8);
         if (row0 + rr < p.Sq && cc * 8 < p.d)
           *reinterpret_cast<uint4*>(gq + (int64_t)rr * p.dq_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
       }
@@ -237,8 +265,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
   //   DKDV: P^T_p / dS^T_p (bf16) overlay G2_p at +0 / +32; dV at 256, dK at 384.  G1_p is dead as soon as
   //         its warpgroup has read it, so S^T of item k+2 is issued before item k is finished.
   //   DQ:   dS (bf16) has four own 32-column buffers at 256 (index 2*((k/2)%2) + p), dQ at 384.
+  //   D = 192: G1_p at 64p, one G2 at 128; P^T_p / dS^T_p (dS_p) overlay G1_p at +0 / +32 (+0);
+  //         DKDV: dV at 192, dK at 320; DQ: dQ at 192.
   constexpr uint32_t C_G1 = 0, C_G2 = 128, C_T = 256;
-  constexpr uint32_t C_ACC1 = (MODE == MODE_DKDV) ? 256 : 384, C_ACC2 = 384;
+  constexpr uint32_t C_ACC1 = BIG ? 192 : ((MODE == MODE_DKDV) ? 256 : 384), C_ACC2 = BIG ? 320 : 384;
+  static_assert(!BIG || C_ACC2 + D <= 512, "tensor memory columns");
 
   if (warp < 8) {
     // =========================== compute warpgroups ===========================
@@ -246,7 +277,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
     const int r = tid & 127;                     // TMEM lane
     const uint32_t lane_field = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tG1 = tmem + lane_field + C_G1 + 64u * pz;
-    const uint32_t tG2 = tmem + lane_field + C_G2 + 64u * pz;
+    const uint32_t tG2 = tmem + lane_field + C_G2 + (BIG ? 0u : 64u * pz);
     const float scale_log2 = p.scale_log2;
     bool ok = true;
 
@@ -292,9 +323,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(Cfg::B_GREAD + pz));
-      const uint32_t tT = (MODE == MODE_DKDV)
-                              ? tG2
-                              : tmem + lane_field + C_T + 32u * (uint32_t)((((k >> 1) & 1) << 1) + pz);
+      const uint32_t tT = BIG ? tG1
+                              : (MODE == MODE_DKDV)
+                                    ? tG2
+                                    : tmem + lane_field + C_T + 32u * (uint32_t)((((k >> 1) & 1) << 1) + pz);
 #include "fm_bwd_sm100_item.inc"
       tc_wait_st();
       tc_fence_before();
@@ -313,9 +345,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
         // warpgroup 0: dK (scaled) staged in the K tile; warpgroup 1: dV staged in the V tile
         const uint32_t tA = tmem + lane_field + (pz == 0 ? C_ACC2 : C_ACC1);
         const float mul = pz == 0 ? p.scale : 1.f;
-        uint8_t* stage = smem + Cfg::OFF_STAT + pz * Cfg::TILE_BYTES;
+        uint8_t* stage = smem + Cfg::OFF_STAT + pz * Cfg::STAT1_BYTES;
+        const int pitch = pz == 0 ? Cfg::W1 * 2 : 256;     // bytes per staged row
+        const int ncol = pz == 0 ? D : DV;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
+          if (32 * c >= ncol) break;
           uint32_t orr[32];
           if (K_items > 0) { tmem_ld32(tA + 32 * c, orr); tc_wait_ld(); }
           else {
@@ -330,7 +365,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
             v.z = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 4]) * mul, __uint_as_float(orr[8 * q4 + 5]) * mul);
             v.w = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 6]) * mul, __uint_as_float(orr[8 * q4 + 7]) * mul);
             const int chunk = 4 * c + q4;
-            *reinterpret_cast<uint4*>(stage + r * 256 + ((chunk ^ (r & 15)) << 4)) = v;
+            *reinterpret_cast<uint4*>(stage + r * pitch + stage_chunk<BIG>(chunk, r)) = v;
           }
         }
         __syncwarp();   // each warp stores the 32 rows it staged itself: no cross-warp dependency
@@ -340,12 +375,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
         const int64_t ld = pz == 0 ? p.dk_s : p.dv_s;
         const int width = pz == 0 ? p.d : p.dv_dim;   // columns past the head dim hold products of zero fill
         const int wrow = (warp & 3) * 32;
+        const int cpr = ncol / 8;                     // 16-byte chunks per row
 #pragma unroll 4
-        for (int x = lane; x < 32 * (D / 8); x += 32) {
-          const int rr = wrow + x / (D / 8), cc = x % (D / 8);
+        for (int x = lane; x < 32 * cpr; x += 32) {
+          const int rr = wrow + x / cpr, cc = x % cpr;
           if (row0 + rr < p.Sk && cc * 8 < width)
             *reinterpret_cast<uint4*>(gout + (int64_t)rr * ld + cc * 8) =
-                *reinterpret_cast<const uint4*>(stage + rr * 256 + ((cc ^ (rr & 15)) << 4));
+                *reinterpret_cast<const uint4*>(stage + rr * pitch + stage_chunk<BIG>(cc, rr));
         }
       } else {
         // both warpgroups: dQ columns [D/2 pz, D/2 pz + D/2), staged in the Q tile
@@ -367,7 +403,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
             v.z = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 4]) * p.scale, __uint_as_float(orr[8 * q4 + 5]) * p.scale);
             v.w = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 6]) * p.scale, __uint_as_float(orr[8 * q4 + 7]) * p.scale);
             const int chunk = (D / 16) * pz + 4 * c + q4;
-            *reinterpret_cast<uint4*>(stage + r * 256 + ((chunk ^ (r & 15)) << 4)) = v;
+            *reinterpret_cast<uint4*>(stage + r * (Cfg::W1 * 2) + stage_chunk<BIG>(chunk, r)) = v;
           }
         }
         __syncwarp();   // warp-local transpose through the staging tile
@@ -378,7 +414,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
           const int rr = wrow + x / (D / 16), cc = (D / 16) * pz + x % (D / 16);
           if (row0 + rr < p.Sq && cc * 8 < p.d)
             *reinterpret_cast<uint4*>(gout + (int64_t)rr * p.dq_s + cc * 8) =
-                *reinterpret_cast<const uint4*>(stage + rr * 256 + ((cc ^ (rr & 15)) << 4));
+                *reinterpret_cast<const uint4*>(stage + rr * (Cfg::W1 * 2) + stage_chunk<BIG>(cc, rr));
         }
       }
       if (tid == 0) PROF(8);
@@ -405,11 +441,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
         if (elect_one()) {
           const uint32_t dst = sRing + slot * Cfg::SLOT_BYTES;
           const uint32_t fb = bar(Cfg::B_RFULL + slot);
-          mbar_arrive_expect_tx(fb, Cfg::SLOT_BYTES * D / 128 + (MODE == MODE_DKDV ? 512 : 0));
-          for (int dc = 0; dc < D / 64; ++dc) {
+          mbar_arrive_expect_tx(fb, (D / 64 + DV / 64) * Cfg::SUB64 + (MODE == MODE_DKDV ? 512 : 0));
+          for (int dc = 0; dc < D / 64; ++dc)
             tma_load_4d(dst + dc * Cfg::SUB64, &tm_str1, fb, dc * 64, hstr, idx * 64, b);
-            tma_load_4d(dst + Cfg::HALF_BYTES + dc * Cfg::SUB64, &tm_str2, fb, dc * 64, hstr, idx * 64, b);
-          }
+          for (int dc = 0; dc < DV / 64; ++dc)
+            tma_load_4d(dst + Cfg::OP1_BYTES + dc * Cfg::SUB64, &tm_str2, fb, dc * 64, hstr, idx * 64, b);
           if (MODE == MODE_DKDV) {
             const int64_t at = ((int64_t)b * p.Hq + hstr) * p.Sq_r + idx * 64;
             const uint32_t ax = sbase + Cfg::OFF_AUX + slot * Cfg::AUX_BYTES;
@@ -431,18 +467,18 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
       // =========================== UMMA issuer ===========================
       if (K_items > 0 && elect_one()) {
         constexpr uint32_t idesc_g = make_idesc(IS_BF16, 128, 64, 0, 0);
-        constexpr uint32_t idesc_acc = make_idesc(IS_BF16, 128, D, 0, 1);
+        constexpr uint32_t idesc_acc1 = make_idesc(IS_BF16, 128, D, 0, 1);    // dK / dQ: N = D
+        constexpr uint32_t idesc_acc2 = make_idesc(IS_BF16, 128, DV, 0, 1);   // dV: N = DV
         bool ok = mbar_wait(bar(Cfg::B_STAT), 0u, wc);
         PROF(2);
         // descriptors are built once; per MMA only a constant is added to the
         // 14-bit address field (all smem offsets are multiples of 16 bytes)
         const uint64_t dA1 = make_sdesc(sStat, 16, 1024);
-        const uint64_t dA2 = make_sdesc(sStat + Cfg::TILE_BYTES, 16, 1024);
+        const uint64_t dA2 = make_sdesc(sStat + Cfg::STAT1_BYTES, 16, 1024);
         const uint64_t dRk = make_sdesc(sRing, 16, 1024);            // K-major view of a ring slot
         const uint64_t dRm = make_sdesc(sRing, Cfg::SUB64, 1024);    // MN-major view of a ring slot
-        // part 1 of the score GEMMs of item k: the first one (S or S^T) runs as soon as the
-        // warpgroup of this parity has READ the previous item out of the score buffers
-        auto issue_g_early = [&](int k) {
+        // first score GEMM of item k (S or S^T, D / 16 k-steps); waits for the ring slot
+        auto issue_g1 = [&](int k) {
           const int slot = k % Cfg::NSLOT, pz = k & 1;
           TRACE(1, 20, k);                    // about to wait for the ring slot
           ok = ok && mbar_wait(bar(Cfg::B_RFULL + slot), (uint32_t)(k / Cfg::NSLOT) & 1u, wc);
@@ -450,53 +486,86 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
           TRACE(1, 21, k);                    // ring slot full
           tc_fence_after();
           const uint64_t db1 = dRk + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));
-          if constexpr (D == 128) umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(tmem + C_G1 + 64u * pz, dA1, db1, idesc_g, 0u);
-          else umma_ss_x4(tmem + C_G1 + 64u * pz, dA1, db1, idesc_g, 0u);
+          const uint32_t dst = tmem + C_G1 + 64u * pz;
+          if constexpr (D >= 128) umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(dst, dA1, db1, idesc_g, 0u);
+          else umma_ss_x4(dst, dA1, db1, idesc_g, 0u);
+          if constexpr (D == 192)
+            umma_ss_x4(dst, dA1 + (uint64_t)(2 * (Cfg::SUB128 >> 4)), db1 + (uint64_t)(2 * (Cfg::SUB64 >> 4)), idesc_g, 1u);
           TRACE(1, 22, k);                    // G issued
         };
-        // part 2: the second score GEMM (dP or dP^T) follows the accumulation MMAs of the
-        // previous item of this parity (in DKDV mode it overwrites the buffer that held
-        // that item's P^T / dS^T)
-        auto issue_g_late = [&](int k) {
-          {
-            const int slot = k % Cfg::NSLOT, pz = k & 1;
-            const uint64_t db2 = dRk + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4) + (Cfg::HALF_BYTES >> 4));
-            if constexpr (D == 128) umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(tmem + C_G2 + 64u * pz, dA2, db2, idesc_g, 0u);
-            else umma_ss_x4(tmem + C_G2 + 64u * pz, dA2, db2, idesc_g, 0u);
-            tc_commit(bar(Cfg::B_GFULL + pz));
-          }
-        };
-        issue_g_early(0); PROF(3); if (ok) issue_g_late(0);
-        if (K_items > 1 && ok) { issue_g_early(1); if (ok) issue_g_late(1); }
-        for (int k = 0; k < K_items && ok; ++k) {
+        // second score GEMM (dP or dP^T, DV / 16 k-steps) and the commit that publishes both
+        auto issue_g2 = [&](int k) {
           const int slot = k % Cfg::NSLOT, pz = k & 1;
-          if (k + 2 < K_items) {
-            ok = mbar_wait(bar(Cfg::B_GREAD + pz), (uint32_t)(k >> 1) & 1u, wc);
-            if (!ok) break;
-            issue_g_early(k + 2);
-            if (!ok) break;
-          }
-          TRACE(1, 23, k);                    // about to wait for T
-          ok = mbar_wait(bar(Cfg::B_TFULL + pz), (uint32_t)(k >> 1) & 1u, wc);
-          if (!ok) break;
-          TRACE(1, 24, k);                    // T ready
-          tc_fence_after();
+          const uint64_t db2 = dRk + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4) + (Cfg::OP1_BYTES >> 4));
+          const uint32_t dst = tmem + C_G2 + (BIG ? 0u : 64u * pz);
+          if constexpr (DV == 128) umma_ss_x8<(Cfg::SUB128 >> 4), (Cfg::SUB64 >> 4)>(dst, dA2, db2, idesc_g, 0u);
+          else umma_ss_x4(dst, dA2, db2, idesc_g, 0u);
+          tc_commit(bar(Cfg::B_GFULL + pz));
+        };
+        // accumulation MMAs of item k; their completion frees the ring slot
+        auto issue_acc = [&](int k) {
+          const int slot = k % Cfg::NSLOT, pz = k & 1;
           const uint64_t dm1 = dRm + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));     // streamed operand 1
-          const uint64_t dm2 = dm1 + (uint64_t)(Cfg::HALF_BYTES >> 4);               // streamed operand 2
+          const uint64_t dm2 = dm1 + (uint64_t)(Cfg::OP1_BYTES >> 4);                // streamed operand 2
           const uint32_t acc_on = k > 0 ? 1u : 0u;
           if (MODE == MODE_DKDV) {
             // dV += P^T dO (streamed operand 2), dK += dS^T Q (streamed operand 1)
-            const uint32_t t1 = tmem + C_G2 + 64u * pz, t2 = t1 + 32u;
-            umma_ts_xn<4>(tmem + C_ACC1, t1, dm2, idesc_acc, acc_on);
-            umma_ts_xn<4>(tmem + C_ACC2, t2, dm1, idesc_acc, acc_on);
+            const uint32_t t1 = tmem + (BIG ? C_G1 : C_G2) + 64u * pz, t2 = t1 + 32u;
+            umma_ts_xn<4>(tmem + C_ACC1, t1, dm2, idesc_acc2, acc_on);
+            umma_ts_xn<4>(tmem + C_ACC2, t2, dm1, idesc_acc1, acc_on);
           } else {
             // dQ += dS K (streamed operand 1)
-            const uint32_t t2 = tmem + C_T + 32u * (uint32_t)((((k >> 1) & 1) << 1) + pz);
-            umma_ts_xn<4>(tmem + C_ACC1, t2, dm1, idesc_acc, acc_on);
+            const uint32_t t2 = BIG ? tmem + C_G1 + 64u * pz
+                                    : tmem + C_T + 32u * (uint32_t)((((k >> 1) & 1) << 1) + pz);
+            umma_ts_xn<4>(tmem + C_ACC1, t2, dm1, idesc_acc1, acc_on);
           }
           tc_commit(bar(Cfg::B_REMPTY + slot));
           TRACE(1, 25, k);                    // ACC issued
-          if (k + 2 < K_items) issue_g_late(k + 2);
+        };
+        if constexpr (!BIG) {
+          // S (S^T) of item k+2 runs as soon as the warpgroup of this parity has READ item k out of the
+          // score buffers; dP (dP^T) follows the accumulation MMAs of item k (in DKDV mode it overwrites
+          // the buffer that held that item's P^T / dS^T)
+          issue_g1(0); PROF(3); if (ok) issue_g2(0);
+          if (K_items > 1 && ok) { issue_g1(1); if (ok) issue_g2(1); }
+          for (int k = 0; k < K_items && ok; ++k) {
+            const int pz = k & 1;
+            if (k + 2 < K_items) {
+              ok = mbar_wait(bar(Cfg::B_GREAD + pz), (uint32_t)(k >> 1) & 1u, wc);
+              if (!ok) break;
+              issue_g1(k + 2);
+              if (!ok) break;
+            }
+            TRACE(1, 23, k);                    // about to wait for T
+            ok = mbar_wait(bar(Cfg::B_TFULL + pz), (uint32_t)(k >> 1) & 1u, wc);
+            if (!ok) break;
+            TRACE(1, 24, k);                    // T ready
+            tc_fence_after();
+            issue_acc(k);
+            if (k + 2 < K_items) issue_g2(k + 2);
+          }
+        } else {
+          // one dP (dP^T) buffer: item k+1's may only be issued once item k's has been read
+          issue_g1(0); PROF(3); if (ok) issue_g2(0);
+          if (K_items > 1 && ok) {
+            issue_g1(1);
+            ok = ok && mbar_wait(bar(Cfg::B_GREAD + 0), 0u, wc);
+            if (ok) issue_g2(1);
+          }
+          for (int k = 0; k < K_items && ok; ++k) {
+            const int pz = k & 1;
+            ok = mbar_wait(bar(Cfg::B_TFULL + pz), (uint32_t)(k >> 1) & 1u, wc);
+            if (!ok) break;
+            tc_fence_after();
+            issue_acc(k);
+            if (k + 2 < K_items) {
+              issue_g1(k + 2);                  // after item k's accumulation MMAs: its overlay is dead
+              if (!ok) break;
+              ok = mbar_wait(bar(Cfg::B_GREAD + (pz ^ 1)), (uint32_t)((k + 1) >> 1) & 1u, wc);
+              if (!ok) break;
+              issue_g2(k + 2);
+            }
+          }
         }
         if (ok) tc_commit(bar(Cfg::B_ACC));
         PROF(6);
@@ -522,14 +591,15 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_stat1, const __grid_cons
 // host
 // ---------------------------------------------------------------------------
 bool bwd_sm100_supported(const fm_attn_args* a) {
-  if (a->d > 128 || a->dv > 128 || a->d % 8 || a->dv % 8) return false;
+  const bool small = a->d <= 128 && a->dv <= 128 && a->d % 8 == 0 && a->dv % 8 == 0;
+  if (!small && !(a->d == 192 && a->dv == 128)) return false;
   if (((uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v | (uintptr_t)a->d_o) & 15) return false;
   return true;
 }
 
-template <bool IS_BF16, int D>
+template <bool IS_BF16, int D, int DV>
 static int launch_bwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
-  using Cfg = BwdSm100Cfg;
+  using Cfg = BwdSm100Cfg<D>;
   FM_REQUIRE((a->Sq + 63) / 64 <= Cfg::LIST_MAX && (a->Sk + 63) / 64 <= Cfg::LIST_MAX, FM_ERR_UNSUPPORTED,
              "backward: Sq=%d / Sk=%d exceed the %d rows this kernel variant indexes", a->Sq, a->Sk,
              Cfg::LIST_MAX * 64);
@@ -546,8 +616,8 @@ static int launch_bwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStr
   FM_TMAP(k64, a->k, a->Sk, a->Hkv, a->d, a->k_stride, 64)
   FM_TMAP(v64, a->v, a->Sk, a->Hkv, a->dv, a->v_stride, 64)
 #undef FM_TMAP
-  auto k1 = bwd_sm100_kernel<MODE_DKDV, IS_BF16, D>;
-  auto k2 = bwd_sm100_kernel<MODE_DQ, IS_BF16, D>;
+  auto k1 = bwd_sm100_kernel<MODE_DKDV, IS_BF16, D, DV>;
+  auto k2 = bwd_sm100_kernel<MODE_DQ, IS_BF16, D, DV>;
   FM_CUDA_TRY(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
   FM_CUDA_TRY(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
   k1<<<dim3((p.Sk + 127) / 128, p.Hkv, p.B), Cfg::NTHREADS, Cfg::SMEM, s>>>(k128, v128, q64, do64, p);
@@ -560,8 +630,9 @@ static int launch_bwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStr
 
 int bwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
   const bool bf = a->dtype == FM_DTYPE_BF16;
-  if (a->d <= 64 && a->dv <= 64) return bf ? launch_bwd_sm100<true, 64>(p, a, s) : launch_bwd_sm100<false, 64>(p, a, s);
-  return bf ? launch_bwd_sm100<true, 128>(p, a, s) : launch_bwd_sm100<false, 128>(p, a, s);
+  if (a->d > 128) return bf ? launch_bwd_sm100<true, 192, 128>(p, a, s) : launch_bwd_sm100<false, 192, 128>(p, a, s);
+  if (a->d <= 64 && a->dv <= 64) return bf ? launch_bwd_sm100<true, 64, 64>(p, a, s) : launch_bwd_sm100<false, 64, 64>(p, a, s);
+  return bf ? launch_bwd_sm100<true, 128, 128>(p, a, s) : launch_bwd_sm100<false, 128, 128>(p, a, s);
 }
 
 #ifdef FM_TRACE

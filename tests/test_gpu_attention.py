@@ -133,8 +133,9 @@ def test_head_dims(kind, d, dv, Hq, Hkv):
 
 @pytest.mark.parametrize("kind", MASKS)
 def test_masks_d192(kind):
-    """Every mask family through the 192 / 128 forward variant of the tcgen05 kernel (two-slot K/V ring,
-    twelve k-steps per score GEMM): GQA, ragged sizes, rows long enough to wrap the ring many times."""
+    """Every mask family through the 192 / 128 variants of the tcgen05 kernels (forward: two-slot K/V ring,
+    twelve k-steps per score GEMM; backward: three-slot ring, single dP buffer, operands written over the
+    score buffer): GQA, ragged sizes, rows long enough to wrap the rings many times."""
     _run(kind, 2, 384, 384, 4, 2, 192, 128, seed=31)
     _run(kind, 1, 1411, 1411, 2, 1, 192, 128, sink=True, seed=32)
     assert _kernel_status() == 0
@@ -219,6 +220,21 @@ def test_deterministic_bitwise(fwd_variant):
         b = run_product(q.cuda(), k.cuda(), v.cuda(), do.cuda(), idx, causal, s, deterministic=True)
         for n in ("out", "lse", "dq", "dk", "dv", "dsink"):
             assert torch.equal(a[n], b[n]), n
+
+
+def test_d192_deterministic_bitwise_and_fp16():
+    """The 192 / 128 backward is the two-kernel variant whatever `deterministic` says: repeated runs are
+    bitwise equal (sink gradient included); fp16 inputs run the same kernels."""
+    idx_np, causal = _mask("share_question", 2, 640, 640, 41)
+    q, k, v, do, s = make_inputs(2, 640, 640, 8, 2, 192, 128, 41, sink=True)
+    idx = torch.from_numpy(np.ascontiguousarray(idx_np).copy()).cuda()
+    a = run_product(q.cuda(), k.cuda(), v.cuda(), do.cuda(), idx, causal, s, deterministic=True)
+    for det in (True, False, True):
+        b = run_product(q.cuda(), k.cuda(), v.cuda(), do.cuda(), idx, causal, s, deterministic=det)
+        for n in ("out", "lse", "dq", "dk", "dv", "dsink"):
+            assert torch.equal(a[n], b[n]), (n, det)
+    _run("causal_doc", 1, 448, 448, 4, 2, 192, 128, seed=42, dtype=torch.float16)
+    assert _kernel_status() == 0
 
 
 @pytest.mark.parametrize("persist", ["0", "1"])
