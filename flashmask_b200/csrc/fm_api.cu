@@ -238,10 +238,10 @@ static int fwd_impl(const fm_attn_args* a, const BlockScore& bs, void* stream) {
                bs.block_ld, p.block_cols);
     p.block_logit = bs.block_logit; p.block_bos = bs.block_bos; p.block_ld = bs.block_ld;
     p.block_log2 = bs.block_size == 32 ? 5 : (bs.block_size == 64 ? 6 : 7);
-    // the tcgen05 kernels have compile-time variants for it; the warp-MMA kernels (head dims above 128,
+    // the tcgen05 kernels have compile-time variants for it; the warp-MMA kernels (head dims 256 and up,
     // or FLASHMASK_B200_FWD=mma) a run-time branch
-    if (a->d <= 128 && fwd_uses_sm100(a->d, a->dv) && fwd_sm100_supported(a)) return fwd_sm100_launch(p, a, (cudaStream_t)stream);
-    FM_REQUIRE(a->d > 128 || !fwd_uses_sm100(a->d, a->dv), FM_ERR_INVALID_ARGUMENT, "fm_fwd_block_score: q/k/v must be 16-byte aligned");
+    if (fwd_uses_sm100(a->d, a->dv) && fwd_sm100_supported(a)) return fwd_sm100_launch(p, a, (cudaStream_t)stream);
+    FM_REQUIRE(!fwd_uses_sm100(a->d, a->dv), FM_ERR_INVALID_ARGUMENT, "fm_fwd_block_score: q/k/v must be 16-byte aligned");
     return fwd_mma_launch(p, a->dtype, (cudaStream_t)stream);
   }
   if (fwd_uses_sm100(a->d, a->dv) && fwd_sm100_supported(a)) return fwd_sm100_launch(p, a, (cudaStream_t)stream);

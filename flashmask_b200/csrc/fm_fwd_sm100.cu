@@ -569,13 +569,10 @@ static int launch_fwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStr
 int fwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s) {
   const bool bf = a->dtype == FM_DTYPE_BF16;
   const bool small = a->d <= 64 && a->dv <= 64;
-  if (a->d == 192) {
-    // 192 / 128: the plain forward only (the block-score side output of this head dim stays on the warp-MMA kernel)
-    FM_REQUIRE(!p.block_logit, FM_ERR_UNSUPPORTED, "forward: no block scores in the 192-column tcgen05 variant");
-    return bf ? launch_fwd_sm100<192, 128, true, 0, false>(p, a, s) : launch_fwd_sm100<192, 128, false, 0, false>(p, a, s);
-  }
 #define FM_FWD_DISPATCH(BSZ, BOS)                                                                         \
   do {                                                                                                    \
+    if (a->d == 192)                                                                                      \
+      return bf ? launch_fwd_sm100<192, 128, true, BSZ, BOS>(p, a, s) : launch_fwd_sm100<192, 128, false, BSZ, BOS>(p, a, s); \
     if (small)                                                                                            \
       return bf ? launch_fwd_sm100<64, 64, true, BSZ, BOS>(p, a, s) : launch_fwd_sm100<64, 64, false, BSZ, BOS>(p, a, s); \
     return bf ? launch_fwd_sm100<128, 128, true, BSZ, BOS>(p, a, s) : launch_fwd_sm100<128, 128, false, BSZ, BOS>(p, a, s); \
