@@ -7,7 +7,8 @@
 Prints ONE JSON line (rank 0).  ``value`` is fwd+bwd effective TFLOP/s counting
 only unmasked (query, key) pairs, summed over all GPUs, with inputs resident in
 HBM; ``e2e`` is the same metric through the public operator with pinned HOST
-buffers (host->device and device->host copies inside the timed region);
+buffers (host->device and device->host copies of every step inside the timed
+region, pipelined over three streams and two buffer sets);
 ``roofline`` describes the dominant kernel; ``cpu_baseline`` is the CPU
 restatement of the reference's dense-mask attention timed on a bounded sample.
 ``--impl reference`` times that CPU implementation alone.
@@ -154,6 +155,61 @@ def time_cpu(step, flops, steps, warmup):
 
 
 # ---------------------------------------------------------------------------
+# end-to-end leg: host buffers in, host buffers out
+# ---------------------------------------------------------------------------
+def e2e_pipelined(compute, host_in, n_steps, dev, sync):
+    """Time `n_steps` steps of `compute` with host buffers on both sides, every copy inside the timed region.
+
+    Each step copies ALL its inputs from pinned host memory into device buffers, runs the public operator
+    (`compute(dict of device tensors) -> tuple of device results`) and copies ALL its results into pinned
+    host memory.  The three phases run on three streams over two buffer sets, the way a caller with host
+    data would drive the operator: the upload of step i+1 and the download of step i-1 overlap the
+    kernels of step i (PCIe carries both directions at once).  Returns (ms per step, d2h bytes per step)."""
+    main = torch.cuda.current_stream(dev)
+    up, down = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    ev = lambda: torch.cuda.Event()
+    slots = [{"inp": {n_: torch.empty_like(t_, device=dev) for n_, t_ in host_in.items()}, "host": None,
+              "keep": None, "up": ev(), "done": ev(), "down": ev()} for _ in range(2)]
+
+    def run(n):
+        for i in range(n):
+            sl = slots[i % 2]
+            if sl["keep"] is not None:
+                up.wait_event(sl["done"])          # the step that read these input buffers has finished
+            with torch.cuda.stream(up):
+                for n_, t_ in host_in.items():
+                    sl["inp"][n_].copy_(t_, non_blocking=True)
+                sl["up"].record(up)
+            main.wait_event(sl["up"])
+            if sl["keep"] is not None:
+                main.wait_event(sl["down"])        # its results have left before their memory is reused
+            outs = compute(sl["inp"])
+            sl["done"].record(main)
+            sl["keep"] = outs
+            if sl["host"] is None:
+                sl["host"] = [torch.empty(o_.shape, dtype=o_.dtype).pin_memory() for o_ in outs]
+            down.wait_event(sl["done"])
+            with torch.cuda.stream(down):
+                for h_, o_ in zip(sl["host"], outs):
+                    h_.copy_(o_, non_blocking=True)
+                sl["down"].record(down)
+        for sl in slots:
+            if sl["keep"] is not None:
+                main.wait_event(sl["down"])
+
+    run(2)
+    sync()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(main)
+    up.wait_event(a)
+    run(n_steps)
+    b.record(main)
+    sync()
+    d2h = sum(h_.numel() * h_.element_size() for h_ in slots[0]["host"])
+    return a.elapsed_time(b) / n_steps, d2h
+
+
+# ---------------------------------------------------------------------------
 # context-parallel leg (N > 1): 128K-token causal-document mask, sequence sharded
 # ---------------------------------------------------------------------------
 def run_cp(args, rank, local_rank, world):
@@ -244,28 +300,19 @@ def run_cp(args, rank, local_rank, world):
 
     e2e = None
     if not args.no_e2e:
-        res = {n_: torch.empty_like(host[n_]).pin_memory() for n_ in ("q", "k", "v", "do")}
-
-        def step_e2e():
-            o, dq, dk, dv = step(*(host[n_].to(dev, non_blocking=True) for n_ in ("q", "k", "v", "do")))
-            res["do"].copy_(o.detach(), non_blocking=True); res["q"].copy_(dq, non_blocking=True)
-            res["k"].copy_(dk, non_blocking=True); res["v"].copy_(dv, non_blocking=True)
-        for _ in range(2):
-            step_e2e()
-        barrier()
-        n_e = max(3, args.steps // 2)
-        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(n_e):
-            step_e2e()
-        b_.record()
-        barrier()
-        te = torch.tensor([a.elapsed_time(b_)], device=dev)
+        def compute(inp):
+            o, dq, dk, dv = step(inp["q"].detach(), inp["k"].detach(), inp["v"].detach(), inp["do"])
+            return o.detach(), dq, dk, dv
+        n_e = max(3, args.steps)
+        ms_e, d2h = e2e_pipelined(compute, host, n_e, dev, barrier)
+        te = torch.tensor([ms_e], device=dev)
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
         nbytes = sum(x.numel() * x.element_size() for x in host.values())
-        e2e = {"value": (fwd_flops + bwd_flops) / (te.item() / n_e * 1e-3) / 1e12, "unit": UNIT,
-               "h2d_bytes_per_step": nbytes * world, "d2h_bytes_per_step": nbytes * world,
-               "ms_per_step": te.item() / n_e}
+        e2e = {"value": (fwd_flops + bwd_flops) / (te.item() * 1e-3) / 1e12, "unit": UNIT,
+               "h2d_bytes_per_step": nbytes * world, "d2h_bytes_per_step": d2h * world,
+               "ms_per_step": te.item(), "steps": n_e,
+               "pipeline": "upload / operator / download on three streams, two buffer sets; every step copies "
+                           "all its inputs and all its results"}
     from flashmask_b200 import cp as cpmod
     n_needed = int(cpmod.shard_need_row(local_mask, S_local, False, world).sum().item())
     peaks = {}
@@ -504,41 +551,30 @@ def main():
                 "bwd_tflops": bwd_flops / (ms_bwd * 1e-3) / 1e12}
 
     # end to end through the public operator with host buffers
-    def step_e2e():
-        qd = host["q"].to(dev, non_blocking=True).requires_grad_(True)
-        kd = host["k"].to(dev, non_blocking=True).requires_grad_(True)
-        vd = host["v"].to(dev, non_blocking=True).requires_grad_(True)
-        dod = host["do"].to(dev, non_blocking=True)
-        idd = idx_host.to(dev, non_blocking=True) if idx_host is not None else None
-        o = fm.flashmask_attention(qd, kd, vd, idd, causal=w.causal, sink=sink, deterministic=det)
-        o.backward(dod)
-        res["out"].copy_(o.detach(), non_blocking=True)
-        res["dq"].copy_(qd.grad, non_blocking=True)
-        res["dk"].copy_(kd.grad, non_blocking=True)
-        res["dv"].copy_(vd.grad, non_blocking=True)
-    res = {"out": torch.empty_like(host["do"]).pin_memory(), "dq": torch.empty_like(host["q"]).pin_memory(),
-           "dk": torch.empty_like(host["k"]).pin_memory(), "dv": torch.empty_like(host["v"]).pin_memory()}
-    h2d = sum(t_.numel() * t_.element_size() for t_ in host.values()) + \
-        (idx_host.numel() * 4 if idx_host is not None else 0)
-    d2h = sum(t_.numel() * t_.element_size() for t_ in res.values())
+    host_in = dict(host)
+    if idx_host is not None:
+        host_in["idx"] = idx_host
+
+    def compute(inp):
+        qd = inp["q"].detach().requires_grad_(True)
+        kd = inp["k"].detach().requires_grad_(True)
+        vd = inp["v"].detach().requires_grad_(True)
+        o = fm.flashmask_attention(qd, kd, vd, inp.get("idx"), causal=w.causal, sink=sink, deterministic=det)
+        o.backward(inp["do"])
+        return o.detach(), qd.grad, kd.grad, vd.grad
+    h2d = sum(t_.numel() * t_.element_size() for t_ in host_in.values())
     e2e = None
     if not args.no_e2e:
-        for _ in range(2):
-            step_e2e()
-        barrier()
-        e_steps = max(3, args.steps // 2)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(e_steps):
-            step_e2e()
-        b.record()
-        barrier()
-        te = torch.tensor([a.elapsed_time(b)], device=dev)
+        e_steps = max(3, args.steps)
+        ms_e, d2h = e2e_pipelined(compute, host_in, e_steps, dev, barrier)
+        te = torch.tensor([ms_e], device=dev)
         if world > 1:
             torch.distributed.all_reduce(te, op=torch.distributed.ReduceOp.MAX)
-        e2e_val = world * (fwd_flops + bwd_flops) / (te.item() / e_steps * 1e-3) / 1e12
+        e2e_val = world * (fwd_flops + bwd_flops) / (te.item() * 1e-3) / 1e12
         e2e = {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "ms_per_step": te.item() / e_steps}
+               "ms_per_step": te.item(), "steps": e_steps,
+               "pipeline": "upload / operator / download on three streams, two buffer sets; every step copies "
+                           "all its inputs (q, k, v, dO, mask) and all its results (O, dQ, dK, dV)"}
 
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
