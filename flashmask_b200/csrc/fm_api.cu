@@ -74,7 +74,7 @@ int option_order_classes() { return g_opt.order_classes; }
 // 128 (multiples of 8); FLASHMASK_B200_FWD=mma forces the warp-MMA variant (A/B runs).
 static bool fwd_uses_sm100(int d, int dv) {
   const bool small = d <= 128 && dv <= 128 && d % 8 == 0 && dv % 8 == 0;
-  if (!small && !(d == 192 && dv == 128)) return false;
+  if (!small && !(d == 192 && dv == 128) && !(d == 256 && dv == 256)) return false;
   return !g_opt.fwd_mma;
 }
 

@@ -1,7 +1,8 @@
 // Forward attention on the 5th-generation tensor cores (tcgen05 / UMMA) for
 // head dims up to 128: a 64-column and a 128-column variant; smaller head dims
 // (multiples of 8) run in the next variant up, the TMA loads filling the
-// columns past the end of a head with zeros.
+// columns past the end of a head with zeros.  Two more variants serve d = 192 /
+// dv = 128 (same plan, 48 KB K tiles, two ring slots) and d = dv = 256 (below).
 //
 // One CTA owns 256 query rows of one (batch, q head) as two 128-row sub-tiles
 // that share every K/V tile.  Warp roles:
@@ -19,6 +20,13 @@
 // maximum grew by more than 2^8 (the rescale is done by the softmax warps
 // themselves).  Every mbarrier wait is bounded: on expiry the CTA raises an
 // abort flag, all roles unwind, TMEM is freed and a status word is set.
+//
+// d = dv = 256: the O accumulator of 128 rows alone needs 256 TMEM columns, so a CTA owns 128 query
+// rows and its two "sub-tiles" are the two 128-column halves of V / O for the SAME rows: both
+// warpgroups run the softmax of the same scores (S is computed once per warpgroup, in its own
+// buffer), warpgroup s accumulates O[:, 128 s : 128 s + 128) = P V[:, 128 s : ...).  One 64 KB Q tile
+// and a two-slot ring of 64 KB K / V tiles.  The score GEMM runs twice per tile (6 MMA units for the
+// 4 the mathematics needs) in exchange for keeping the plan, the barriers and the tile body above.
 #include <type_traits>
 
 #include "fm_attn_params.cuh"
@@ -40,9 +48,12 @@ __device__ long long g_fprof[64 * 8];
 #define FPROF_VAL(slot, v)
 #endif
 
-// D: width q / k are computed at (64, 128 or 192), DV: width of v / o (64 or 128).
+// D: width q / k are computed at (64, 128, 192 or 256), DV: width of v / o (64, 128 or 256).
 template <int D, int DV = D>
 struct FwdSm100Cfg {
+  static constexpr bool SPLITV = D == 256;              // sub-tiles are halves of V / O, not of the rows
+  static constexpr int ROWS = SPLITV ? 128 : 256;       // query rows per CTA
+  static constexpr int DVS = SPLITV ? DV / 2 : DV;      // O columns per warpgroup
   // the 64-column variant doubles the ring depth: its slots are half as large; the 192-column one has room
   // for two slots (one K tile and one V tile in flight) beside its two 48 KB Q sub-tiles
   static constexpr int BM = 128, BN = 128, NSTAGE = (D == 64 ? 8 : (D > 128 ? 2 : 4)), NBND = 2, LIST_MAX = 2048;
@@ -53,7 +64,7 @@ struct FwdSm100Cfg {
   static constexpr int SLOT_BYTES = K_BYTES > V_BYTES ? K_BYTES : V_BYTES;
   static constexpr int BND_BYTES = 128 * 4 * 4;
   static constexpr int OFF_Q = 0;
-  static constexpr int OFF_KV = OFF_Q + 2 * Q_BYTES;
+  static constexpr int OFF_KV = OFF_Q + (SPLITV ? 1 : 2) * Q_BYTES;
   static constexpr int OFF_BND = OFF_KV + NSTAGE * SLOT_BYTES;
   static constexpr int OFF_LIST = OFF_BND + NBND * BND_BYTES;
   static constexpr int OFF_BAR = OFF_LIST + LIST_MAX * 4;
@@ -67,7 +78,8 @@ struct FwdSm100Cfg {
   static constexpr int B_QFULL = 0, B_KVFULL = 2, B_KVEMPTY = 2 + NSTAGE, B_SFULL = 2 + 2 * NSTAGE,
                        B_PFULL = B_SFULL + 2, B_ODONE = B_PFULL + 2, B_BNDFULL = B_ODONE + 2,
                        B_BNDEMPTY = B_BNDFULL + NBND, B_COUNT = B_BNDEMPTY + NBND;
-  static_assert((D == 64 && DV == 64) || (D == 128 && DV == 128) || (D == 192 && DV == 128), "head-dim variants");
+  static_assert((D == 64 && DV == 64) || (D == 128 && DV == 128) || (D == 192 && DV == 128) ||
+                    (D == 256 && DV == 256), "head-dim variants");
   static_assert(SMEM_BS <= 227 * 1024 && SMEM <= 227 * 1024, "shared memory");
   static_assert(B_COUNT <= 32, "barrier storage");
   static_assert(NSTAGE * SLOT_BYTES >= LIST_MAX * 8 * 4, "the ring stages the reductions of the list build");
@@ -83,6 +95,8 @@ __global__ void __launch_bounds__(384, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const AttnKParams p) {
   using Cfg = FwdSm100Cfg<D, DV>;
+  constexpr bool SPLITV = Cfg::SPLITV;
+  constexpr int ROWS = Cfg::ROWS, DVS = Cfg::DVS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
@@ -99,16 +113,16 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (tid == 0) FPROF(0);
   // descriptor fetches start before anything else: the first loads wait on them
   if (warp == 8 && lane == 0) { tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); }
-  const int n_tiles = (p.Sq + 255) / 256;
+  const int n_tiles = (p.Sq + ROWS - 1) / ROWS;
   int t = n_tiles - 1 - blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
-  if (p.fwd_order) {
+  if (!SPLITV && p.fwd_order) {
     const OrderedCta c = ordered_cta(p.fwd_order, p.Hq);
     t = c.unit; hq = c.head; b = c.b;
   }
   const int hk = hq / (p.Hq / p.Hkv);
   const MaskDesc& md = p.md;
   const int bh_mask = md.ncols ? ((md.mask_B == 1 ? 0 : b) * md.Hm + hq / (p.Hq / md.Hm)) : 0;
-  const int ms = t * 256;
+  const int ms = t * ROWS;
   const int off = p.Sk - p.Sq;
 
   if (tid == 0) misc[4] = 0;
@@ -122,7 +136,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     fence_mbar_init();
     // both Q sub-tiles are requested right away: the loads overlap with the
     // list build (rows past the end of the sequence arrive as zeros)
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < (SPLITV ? 1 : 2); ++s) {
       mbar_arrive_expect_tx(bar(Cfg::B_QFULL + s), Cfg::Q_BYTES);
       for (int dc = 0; dc < D / 64; ++dc)
         tma_load_4d(sQ + s * Cfg::Q_BYTES + dc * Cfg::SUB, &tm_q, bar(Cfg::B_QFULL + s), dc * 64, hq,
@@ -136,7 +150,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (warp == 10) {
     // surviving K tiles, right to left, with the flags of both sub-tiles
     const int nb = (p.Sk + 127) / 128;
-    const int me_tile = min(ms + 256, p.Sq);
+    const int me_tile = min(ms + ROWS, p.Sq);
     int n_hi = nb;
     if (md.causal) n_hi = max(0, min(nb, (me_tile + off + 127) / 128));
     int cnt = 0, c0 = 0, c1 = 0;
@@ -148,7 +162,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       uint32_t f0 = 0, f1 = 0;
       if (n >= 0) {
         f0 = tile_flags(mst, 0, n, ms, min(ms + 128, p.Sq), 128);
-        if (ms + 128 < p.Sq) f1 = tile_flags(mst, 0, n, ms + 128, min(ms + 256, p.Sq), 128);
+        if (SPLITV) f1 = f0;
+        else if (ms + 128 < p.Sq) f1 = tile_flags(mst, 0, n, ms + 128, min(ms + 256, p.Sq), 128);
       }
       const bool keep = (f0 | f1) != 0;
       const uint32_t bal = __ballot_sync(0xffffffffu, keep);
@@ -174,17 +189,17 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // tensor memory is returned before leaving
     if (warp == 8 && lane == 0) {
       mbar_wait(bar(Cfg::B_QFULL + 0), 0u, wc);
-      mbar_wait(bar(Cfg::B_QFULL + 1), 0u, wc);
+      if (!SPLITV) mbar_wait(bar(Cfg::B_QFULL + 1), 0u, wc);
     }
     if (warp == 9) tmem_dealloc(tmem, 512);
     uint16_t* go = reinterpret_cast<uint16_t*>(p.o) + b * p.o_b + (int64_t)ms * p.o_s + hq * p.o_h;
-    for (int x = tid; x < 256 * (DV / 8); x += Cfg::NTHREADS) {
+    for (int x = tid; x < ROWS * (DV / 8); x += Cfg::NTHREADS) {
       const int rr = x / (DV / 8), cc = x % (DV / 8);
       if (ms + rr < p.Sq && cc * 8 < p.dv_dim)
         *reinterpret_cast<uint4*>(go + (int64_t)rr * p.o_s + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
     }
     const float empty_lse = p.sink ? p.sink[hq] : neg_inf();
-    for (int rr = tid; rr < 256; rr += Cfg::NTHREADS)
+    for (int rr = tid; rr < ROWS; rr += Cfg::NTHREADS)
       if (ms + rr < p.Sq) p.lse[((int64_t)b * p.Hq + hq) * p.Sq + ms + rr] = empty_lse;
     return;
   }
@@ -195,7 +210,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     setmaxnreg_inc<216>();
     const int s = warp >> 2;
     const int r = tid & 127;                   // row inside the sub-tile == TMEM lane
-    const int row = ms + 128 * s + r;
+    const int row = ms + (SPLITV ? 0 : 128 * s) + r;
     const uint32_t lane_field = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + lane_field + 128u * s;
     const uint32_t tP = tS + 64u;
@@ -217,7 +232,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     int bs_bos = 0, bs_pend_lo = INT_MAX, bs_pend_hi = -1;    // pending groups [lo, hi]; lo > hi: none
     bool bs_vec = false;
     if constexpr (BLOCK_SCORE != 0) {
-      if (row < p.Sq) bs_dst = p.block_logit + (((int64_t)b * p.Hq + hq) * p.Sq + row) * p.block_ld;
+      // (d = 256: both warpgroups see the same scores; warpgroup 0 writes them)
+      if (row < p.Sq && !(SPLITV && s == 1))
+        bs_dst = p.block_logit + (((int64_t)b * p.Hq + hq) * p.Sq + row) * p.block_ld;
       if constexpr (BLOCK_BOS) {
         bs_acc = reinterpret_cast<float*>(smem + Cfg::OFF_BS) + tid;
 #pragma unroll
@@ -313,9 +330,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       float l_tot = l_run;
       if (p.sink) l_tot += fast_exp2(p.sink[hq] * kLog2e - m_fin);
       const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-      uint8_t* stage = smem + Cfg::OFF_Q + s * Cfg::Q_BYTES;   // Q_s is no longer needed
+      uint8_t* stage = smem + Cfg::OFF_Q + (SPLITV ? 0 : s * Cfg::Q_BYTES);   // Q is no longer needed
+      constexpr int CH0 = SPLITV ? DVS / 8 : 0;          // d = 256: warpgroup s stages chunks [16 s, 16 s + 16)
 #pragma unroll
-      for (int c = 0; c < DV / 32; ++c) {
+      for (int c = 0; c < DVS / 32; ++c) {
         uint32_t orr[32];
         if (n_done > 0) {
           tmem_ld32(tO + 32 * c, orr);
@@ -331,20 +349,21 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           v.y = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 2]) * inv, __uint_as_float(orr[8 * q4 + 3]) * inv);
           v.z = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 4]) * inv, __uint_as_float(orr[8 * q4 + 5]) * inv);
           v.w = pack2<IS_BF16>(__uint_as_float(orr[8 * q4 + 6]) * inv, __uint_as_float(orr[8 * q4 + 7]) * inv);
-          const int chunk = 4 * c + q4;                 // 16-byte chunk inside the row
+          const int chunk = CH0 * s + 4 * c + q4;       // 16-byte chunk inside the row
           *reinterpret_cast<uint4*>(stage + r * (DV * 2) + ((chunk ^ (r & (DV / 8 - 1))) << 4)) = v;
         }
       }
-      if (row < p.Sq)
+      if (row < p.Sq && !(SPLITV && s == 1))
         p.lse[((int64_t)b * p.Hq + hq) * p.Sq + row] = l_tot > 0.f ? (m_fin + log2f(l_tot)) * kLn2 : neg_inf();
       __syncwarp();   // each warp stores the 32 rows it staged itself: no cross-warp dependency
-      uint16_t* go = reinterpret_cast<uint16_t*>(p.o) + b * p.o_b + (int64_t)(ms + 128 * s) * p.o_s + hq * p.o_h;
-      constexpr int CH = DV / 8;
+      const int rbase = ms + (SPLITV ? 0 : 128 * s);
+      uint16_t* go = reinterpret_cast<uint16_t*>(p.o) + b * p.o_b + (int64_t)rbase * p.o_s + hq * p.o_h;
+      constexpr int CH = DV / 8, CHW = DVS / 8;          // chunks per row, chunks this warpgroup staged
       const int wrow = (warp & 3) * 32;
 #pragma unroll 4
-      for (int idx = lane; idx < 32 * CH; idx += 32) {
-        const int rr = wrow + idx / CH, cc = idx % CH;
-        if (ms + 128 * s + rr < p.Sq && cc * 8 < p.dv_dim) {
+      for (int idx = lane; idx < 32 * CHW; idx += 32) {
+        const int rr = wrow + idx / CHW, cc = CH0 * s + idx % CHW;
+        if (rbase + rr < p.Sq && cc * 8 < p.dv_dim) {
           const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * (DV * 2) + ((cc ^ (rr & (CH - 1))) << 4));
           *reinterpret_cast<uint4*>(go + (int64_t)rr * p.o_s + cc * 8) = v;
         }
@@ -387,12 +406,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
       }
       // a sub-tile without work never consumed its Q load: make sure it has landed
-      if (ok && lane == 0) { mbar_wait(bar(Cfg::B_QFULL + 0), 0u, wc); mbar_wait(bar(Cfg::B_QFULL + 1), 0u, wc); }
+      if (ok && lane == 0) { mbar_wait(bar(Cfg::B_QFULL + 0), 0u, wc); if (!SPLITV) mbar_wait(bar(Cfg::B_QFULL + 1), 0u, wc); }
     } else if (warp == 9) {
       // =========================== UMMA issuer ===========================
       if (elect_one()) {
         constexpr uint32_t idesc_qk = make_idesc(IS_BF16, 128, 128, 0, 0);
-        constexpr uint32_t idesc_pv = make_idesc(IS_BF16, 128, DV, 0, 1);
+        constexpr uint32_t idesc_pv = make_idesc(IS_BF16, 128, DVS, 0, 1);
         int npv[2] = {0, 0};
         bool q_ready[2] = {false, false};
         bool ok = true;
@@ -405,10 +424,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             constexpr int s = decltype(sub)::value;   // compile-time: the per-sub-tile counters stay in registers
           const int k = 2 * i, slot = k % Cfg::NSTAGE;
           ok = ok && mbar_wait(bar(Cfg::B_KVFULL + slot), (uint32_t)(k / Cfg::NSTAGE) & 1u, wc);
-          if (ok && !q_ready[s]) { ok = mbar_wait(bar(Cfg::B_QFULL + s), 0u, wc); q_ready[s] = true; }
+          if (ok && !q_ready[s]) { ok = mbar_wait(bar(Cfg::B_QFULL + (SPLITV ? 0 : s)), 0u, wc); q_ready[s] = true; }
           if (!ok) return;
           tc_fence_after();
-          const uint64_t da = dq0 + (uint64_t)(s * (Cfg::Q_BYTES >> 4));
+          const uint64_t da = dq0 + (uint64_t)(SPLITV ? 0 : s * (Cfg::Q_BYTES >> 4));
           const uint64_t db = dk0 + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));
           const uint32_t dst = tmem + 128u * s;
           if constexpr (D == 128) umma_ss_x8<(Cfg::SUB >> 4), (Cfg::SUB >> 4)>(dst, da, db, idesc_qk, 0u);
@@ -416,6 +435,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             // three 64-column sub-tiles of q / k: eight k-steps, then four more on top
             umma_ss_x8<(Cfg::SUB >> 4), (Cfg::SUB >> 4)>(dst, da, db, idesc_qk, 0u);
             umma_ss_x4(dst, da + (uint64_t)(2 * (Cfg::SUB >> 4)), db + (uint64_t)(2 * (Cfg::SUB >> 4)), idesc_qk, 1u);
+          } else if constexpr (D == 256) {
+            // four 64-column sub-tiles: eight k-steps over the first two, eight over the last two
+            umma_ss_x8<(Cfg::SUB >> 4), (Cfg::SUB >> 4)>(dst, da, db, idesc_qk, 0u);
+            umma_ss_x8<(Cfg::SUB >> 4), (Cfg::SUB >> 4)>(dst, da + (uint64_t)(2 * (Cfg::SUB >> 4)),
+                                                         db + (uint64_t)(2 * (Cfg::SUB >> 4)), idesc_qk, 1u);
           } else umma_ss_x4(dst, da, db, idesc_qk, 0u);
           tc_commit(bar(Cfg::B_SFULL + s));
         };
@@ -426,7 +450,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ok = ok && mbar_wait(bar(Cfg::B_PFULL + s), (uint32_t)npv[s] & 1u, wc);
           if (!ok) return;
           tc_fence_after();
-          const uint64_t db = dv0 + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4));
+          // (d = 256: warpgroup s owns V columns [128 s, 128 s + 128): sub-tiles 2 s and 2 s + 1 of the V tile)
+          const uint64_t db = dv0 + (uint64_t)(slot * (Cfg::SLOT_BYTES >> 4) + (SPLITV ? s * 2 * (Cfg::SUB >> 4) : 0));
           const uint32_t dst = tmem + 256u + 128u * s, src = tmem + 128u * s + 64u;
           const uint32_t acc0 = npv[s] > 0 ? 1u : 0u;
           umma_ts_xn<8>(dst, src, db, idesc_pv, acc0);
@@ -541,7 +566,7 @@ int bounded_wait_selftest_launch(uint64_t budget_ns, cudaStream_t s) {
 
 bool fwd_sm100_supported(const fm_attn_args* a) {
   const bool small = a->d <= 128 && a->dv <= 128 && a->d % 8 == 0 && a->dv % 8 == 0;
-  if (!small && !(a->d == 192 && a->dv == 128)) return false;
+  if (!small && !(a->d == 192 && a->dv == 128) && !(a->d == 256 && a->dv == 256)) return false;
   if (((uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v) & 15) return false;
   return true;
 }
@@ -559,7 +584,7 @@ static int launch_fwd_sm100(const AttnKParams& p, const fm_attn_args* a, cudaStr
   auto kern = fwd_sm100_kernel<D, DV, IS_BF16, BLOCK_SCORE, BLOCK_BOS>;
   constexpr int smem_bytes = BLOCK_BOS ? Cfg::SMEM_BS : Cfg::SMEM;
   FM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-  dim3 grid((p.Sq + 255) / 256, p.Hq, p.B);
+  dim3 grid((p.Sq + Cfg::ROWS - 1) / Cfg::ROWS, p.Hq, p.B);
   kern<<<grid, Cfg::NTHREADS, smem_bytes, s>>>(tq, tk, tv, p);
   count_launches(1);
   FM_CUDA_TRY(cudaGetLastError());
@@ -571,6 +596,8 @@ int fwd_sm100_launch(const AttnKParams& p, const fm_attn_args* a, cudaStream_t s
   const bool small = a->d <= 64 && a->dv <= 64;
 #define FM_FWD_DISPATCH(BSZ, BOS)                                                                         \
   do {                                                                                                    \
+    if (a->d == 256)                                                                                      \
+      return bf ? launch_fwd_sm100<256, 256, true, BSZ, BOS>(p, a, s) : launch_fwd_sm100<256, 256, false, BSZ, BOS>(p, a, s); \
     if (a->d == 192)                                                                                      \
       return bf ? launch_fwd_sm100<192, 128, true, BSZ, BOS>(p, a, s) : launch_fwd_sm100<192, 128, false, BSZ, BOS>(p, a, s); \
     if (small)                                                                                            \

@@ -142,6 +142,15 @@ def test_masks_d192(kind):
 
 
 @pytest.mark.parametrize("kind", MASKS)
+def test_masks_d256(kind):
+    """Every mask family through the 256 / 256 forward variant of the tcgen05 kernel (128 query rows per CTA, the
+    two warpgroups own the two 128-column halves of V / O); the backward of this head dim is the warp-MMA one."""
+    _run(kind, 2, 384, 384, 4, 2, 256, 256, seed=51)
+    _run(kind, 1, 1411, 1411, 2, 1, 256, 256, sink=True, seed=52)
+    assert _kernel_status() == 0
+
+
+@pytest.mark.parametrize("kind", MASKS)
 def test_masks_d64(kind, fwd_variant):
     """Every mask family through the 64-column variants: GQA, rows long enough to wrap the K/V ring."""
     _run(kind, 2, 384, 384, 4, 2, 64, 64, seed=21)
