@@ -99,9 +99,22 @@ def _run(kind, B, Sq, Sk, Hq, Hkv, d, dv, sink=False, seed=0, dtype=torch.bfloat
     assert_parity(got, ref, lowp, label=f"{kind}: ")
     assert_lse(got, ref)
     if sink:
-        err = (got["dsink"].float().cpu() - ref["dsink"]).abs().max().item()
         scale = ref["dsink"].abs().max().item() + 1.0
-        assert err <= 1e-2 + 2 * 2 ** -8 * scale, f"dsink err {err}"
+        # the kernel against its own definition, evaluated on the tensors it read (the bf16 O and the LSE of this
+        # forward): dsink[h] = -sum_{b,i} exp(sink[h] - lse[b,h,i]) * rowsum(O * dO)[b,i,h]
+        dps = (got["out"].float() * doc.float()).sum(-1).permute(0, 2, 1)
+        own = -(torch.exp(s.cuda()[None, :, None] - got["lse"].float()) * dps).sum((0, 2))
+        err_own = (got["dsink"].float() - own).abs().max().item()
+        assert err_own <= 1e-3 + 2 ** -10 * scale, f"dsink vs its definition: {err_own}"
+        # and against the fp32 oracle: what is left is the rounding of O to 16 bits before rowsum(O * dO), which
+        # the reference's preprocess kernel has too and which grows with the width of the row
+        # (noise model: every element of O carries a relative rounding error of up to 2^-9, independent
+        # between elements; four standard deviations of the resulting sum, per head)
+        w2 = torch.exp(s[None, :, None] - ref["lse"].float()) ** 2
+        var = (w2 * ((ref["out"].float() * do.float()) ** 2).sum(-1).permute(0, 2, 1)).sum((0, 2))
+        tol = 1e-2 + 4 * 2 ** -9 * var.sqrt()
+        err = (got["dsink"].float().cpu() - ref["dsink"]).abs()
+        assert (err <= tol).all(), f"dsink err {err.tolist()} > {tol.tolist()}"
     return got, ref
 
 
