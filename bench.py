@@ -565,7 +565,7 @@ def main():
     h2d = sum(t_.numel() * t_.element_size() for t_ in host_in.values())
     e2e = None
     if not args.no_e2e:
-        e_steps = max(3, args.steps)
+        e_steps = max(6, 2 * args.steps)      # the two-step ramp of the pipeline weighs less over more steps
         ms_e, d2h = e2e_pipelined(compute, host_in, e_steps, dev, barrier)
         te = torch.tensor([ms_e], device=dev)
         if world > 1:

@@ -266,14 +266,16 @@ static bool order_geometry_any(const fm_attn_args* a, int which, OrderGeom* g) {
   if (!a || a->ncols == 0 || a->Sq <= 0 || a->Sk <= 0 || a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0) return false;
   if (!(a->Hm == 1 || a->Hm == a->Hkv) || !(a->mask_B == 1 || a->mask_B == a->B) || a->Hq % a->Hkv) return false;
   const int nk = (a->Sk + 127) / 128;
+  // (the 256-column forward owns 128 rows per CTA and takes no table; the 192-column backward runs the
+  // one-unit kernels, which take none either)
   if (which == FM_ORDER_FWD) {
-    if (!fwd_uses_sm100(a->d, a->dv)) return false;
+    if (!fwd_uses_sm100(a->d, a->dv) || a->d > 192) return false;
     *g = OrderGeom{0, 256, (a->Sq + 255) / 256, nk, a->Hq};
   } else if (which == FM_ORDER_BWD_DQ) {
-    if (!bwd_uses_sm100(a->d, a->dv)) return false;
+    if (!bwd_uses_sm100(a->d, a->dv) || a->d > 128) return false;
     *g = OrderGeom{0, 128, (a->Sq + 127) / 128, nk, a->Hq};
   } else if (which == FM_ORDER_BWD_DKDV) {
-    if (!bwd_uses_sm100(a->d, a->dv)) return false;
+    if (!bwd_uses_sm100(a->d, a->dv) || a->d > 128) return false;
     *g = OrderGeom{1, 64, nk, (a->Sq + 63) / 64, a->Hkv};
   } else {
     return false;
