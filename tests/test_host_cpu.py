@@ -54,6 +54,27 @@ def test_argument_errors_need_no_gpu():
         fm.flashmask_attention(q, q, q)
 
 
+def test_kernel_variant_routing_needs_no_gpu():
+    """Tile shapes and launch tables by head dim: the tcgen05 variants (128-column K tiles; 64-query items in the
+    backward) serve every head dim up to 128, 192 / 128 in both directions and the 256 / 256 forward; a launch
+    table exists only where the variant walks one (not for the 256 forward, not for the 192 backward)."""
+    for d, dv in [(8, 8), (64, 64), (96, 80), (128, 128), (192, 128), (256, 256)]:
+        assert fm.fwd_tile_shape(d, dv) == (128, 128), (d, dv)
+    for d, dv in [(64, 64), (128, 64), (128, 128), (192, 128)]:
+        assert fm.bwd_tile_shape(d, dv) == (64, 128), (d, dv)
+    assert fm.bwd_tile_shape(256, 256) != (64, 128) and fm.bwd_tile_shape(576, 512) != (64, 128)
+    lib = _lib.load()
+    a = _lib.AttnArgs()
+    a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.Hm, a.mask_B, a.ncols = 2, 4096, 4096, 8, 2, 1, 2, 2
+    want = {(128, 128): (True, True, True), (64, 64): (True, True, True), (192, 128): (True, False, False),
+            (256, 256): (False, False, False), (576, 512): (False, False, False)}
+    for (d, dv), has in want.items():
+        a.d, a.dv = d, dv
+        got = tuple(lib.fm_launch_order_ints(ctypes.byref(a), w) > 0 for w in
+                    (_lib.FM_ORDER_FWD, _lib.FM_ORDER_BWD_DQ, _lib.FM_ORDER_BWD_DKDV))
+        assert got == has, (d, dv, got)
+
+
 def test_struct_layout_matches_header():
     # 18 int32/float + 15 pointers/size_t + 24 int64
     assert ctypes.sizeof(_lib.AttnArgs) == 18 * 4 + 15 * 8 + 24 * 8 + 3 * 8
