@@ -65,6 +65,11 @@ struct FwdSm100Cfg {
   static constexpr int BND_BYTES = 128 * 4 * 4;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_KV = OFF_Q + (SPLITV ? 1 : 2) * Q_BYTES;
+  // Causal masks: the K and V tiles of the diagonal (the first tile of the list, right to left) are requested at
+  // kernel entry into slots 0 and 1, before the list exists, where the ring is deep enough to keep the list
+  // build's staging area (64 KB) clear of those two slots.
+  static constexpr bool SPEC = NSTAGE >= 4 && NSTAGE * SLOT_BYTES >= 128 * 1024 && 2 * SLOT_BYTES <= 64 * 1024;
+  static constexpr int OFF_STAGE = OFF_KV + (SPEC ? 64 * 1024 : 0);
   static constexpr int OFF_BND = OFF_KV + NSTAGE * SLOT_BYTES;
   static constexpr int OFF_LIST = OFF_BND + NBND * BND_BYTES;
   static constexpr int OFF_BAR = OFF_LIST + LIST_MAX * 4;
@@ -82,7 +87,7 @@ struct FwdSm100Cfg {
                     (D == 256 && DV == 256), "head-dim variants");
   static_assert(SMEM_BS <= 227 * 1024 && SMEM <= 227 * 1024, "shared memory");
   static_assert(B_COUNT <= 32, "barrier storage");
-  static_assert(NSTAGE * SLOT_BYTES >= LIST_MAX * 8 * 4, "the ring stages the reductions of the list build");
+  static_assert(OFF_STAGE + LIST_MAX * 8 * 4 <= OFF_BND, "the ring stages the reductions of the list build");
   static_assert(SMEM > 120 * 1024, "one CTA per SM is assumed by the 512-column TMEM allocation");
 };
 
@@ -124,6 +129,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int bh_mask = md.ncols ? ((md.mask_B == 1 ? 0 : b) * md.Hm + hq / (p.Hq / md.Hm)) : 0;
   const int ms = t * ROWS;
   const int off = p.Sk - p.Sq;
+  // first K tile right of everything these rows can see, and whether the diagonal tile is loaded ahead of the list
+  const int nb = (p.Sk + 127) / 128;
+  const int n_hi = md.causal ? max(0, min(nb, (min(ms + ROWS, p.Sq) + off + 127) / 128)) : nb;
+  const bool spec = Cfg::SPEC && BLOCK_SCORE == 0 && md.causal && n_hi > 0;
 
   if (tid == 0) misc[4] = 0;
   if (warp == 8 && lane == 0) {
@@ -142,6 +151,15 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         tma_load_4d(sQ + s * Cfg::Q_BYTES + dc * Cfg::SUB, &tm_q, bar(Cfg::B_QFULL + s), dc * 64, hq,
                     ms + 128 * s, b);
     }
+    if (spec) {
+      const int j0 = (n_hi - 1) * 128;
+      mbar_arrive_expect_tx(bar(Cfg::B_KVFULL + 0), Cfg::K_BYTES);
+      for (int dc = 0; dc < D / 64; ++dc)
+        tma_load_4d(sKV + dc * Cfg::SUB, &tm_k, bar(Cfg::B_KVFULL + 0), dc * 64, hk, j0, b);
+      mbar_arrive_expect_tx(bar(Cfg::B_KVFULL + 1), Cfg::V_BYTES);
+      for (int dc = 0; dc < DV / 64; ++dc)
+        tma_load_4d(sKV + Cfg::SLOT_BYTES + dc * Cfg::SUB, &tm_v, bar(Cfg::B_KVFULL + 1), dc * 64, hk, j0, b);
+    }
   }
   if (warp == 9) {
     tmem_alloc(sbase + Cfg::OFF_MISC, 512);
@@ -149,13 +167,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
   if (warp == 10) {
     // surviving K tiles, right to left, with the flags of both sub-tiles
-    const int nb = (p.Sk + 127) / 128;
-    const int me_tile = min(ms + ROWS, p.Sq);
-    int n_hi = nb;
-    if (md.causal) n_hi = max(0, min(nb, (me_tile + off + 127) / 128));
     int cnt = 0, c0 = 0, c1 = 0;
     // the reductions the classification needs are staged in the (still idle) K/V ring
-    const MaskDesc mst = stage_minmax(md, bh_mask, 0, n_hi, reinterpret_cast<int32_t*>(smem + Cfg::OFF_KV),
+    const MaskDesc mst = stage_minmax(md, bh_mask, 0, n_hi, reinterpret_cast<int32_t*>(smem + Cfg::OFF_STAGE),
                                       Cfg::LIST_MAX, lane);
     for (int base = n_hi - 1; base >= 0; base -= 32) {
       const int n = base - lane;
@@ -164,6 +178,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         f0 = tile_flags(mst, 0, n, ms, min(ms + 128, p.Sq), 128);
         if (SPLITV) f1 = f0;
         else if (ms + 128 < p.Sq) f1 = tile_flags(mst, 0, n, ms + 128, min(ms + 256, p.Sq), 128);
+        if (spec && n == n_hi - 1 && (f0 | f1) == 0) {
+          // the diagonal tile is already on its way into slots 0 / 1, so it is the first list entry whatever its
+          // class: an invisible one is computed with the element mask (every score masked, P = 0)
+          f0 = FM_TF_ACTIVE | FM_TF_CAUSAL | FM_TF_RAGGED | (md.ncols ? FM_TF_BOUNDS : 0u);
+          if (ms + 128 < p.Sq) f1 = f0;
+        }
       }
       const bool keep = (f0 | f1) != 0;
       const uint32_t bal = __ballot_sync(0xffffffffu, keep);
@@ -379,7 +399,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       for (int i = 0; i < cnt && ok; ++i) {
         const uint32_t e = list[i];
         const int j0 = (int)(e & 0xFFFFu) * 128;
-        if (elect_one()) {
+        if (!(spec && i == 0) && elect_one()) {       // (the first tile of a causal mask was requested at entry)
           for (int kv = 0; kv < 2 && ok; ++kv) {
             const int k = 2 * i + kv, slot = k % Cfg::NSTAGE;
             const uint32_t par = ((uint32_t)(k / Cfg::NSTAGE) & 1u) ^ 1u;
