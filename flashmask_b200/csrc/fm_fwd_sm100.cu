@@ -39,10 +39,13 @@ using namespace sm100;
 __device__ int g_fwd_status = 0;
 
 #ifdef FM_TRACE
-// Debug build only: clock stamps at the phase boundaries of CTAs (x < 64, y = 0, z = 0).
-__device__ long long g_fprof[64 * 8];
-#define FPROF(slot) do { if (blockIdx.y == 0 && blockIdx.z == 0 && blockIdx.x < 64) g_fprof[blockIdx.x * 8 + (slot)] = clock64(); } while (0)
-#define FPROF_VAL(slot, v) do { if (blockIdx.y == 0 && blockIdx.z == 0 && blockIdx.x < 64) g_fprof[blockIdx.x * 8 + (slot)] = (v); } while (0)
+// Debug build only: clock stamps at the phase boundaries of CTAs (x < 64, y = FM_TRACE_Y, z = 0).
+#ifndef FM_TRACE_Y
+#define FM_TRACE_Y 0
+#endif
+__device__ long long g_fprof[64 * 16];
+#define FPROF(slot) do { if (blockIdx.y == FM_TRACE_Y && blockIdx.z == 0 && blockIdx.x < 64) g_fprof[blockIdx.x * 16 + (slot)] = clock64(); } while (0)
+#define FPROF_VAL(slot, v) do { if (blockIdx.y == FM_TRACE_Y && blockIdx.z == 0 && blockIdx.x < 64) g_fprof[blockIdx.x * 16 + (slot)] = (v); } while (0)
 #else
 #define FPROF(slot)
 #define FPROF_VAL(slot, v)
@@ -125,6 +128,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     t = c.unit; hq = c.head; b = c.b;
   }
   const int hk = hq / (p.Hq / p.Hkv);
+  if (tid == 0) FPROF(8);                    // table entry known
   const MaskDesc& md = p.md;
   const int bh_mask = md.ncols ? ((md.mask_B == 1 ? 0 : b) * md.Hm + hq / (p.Hq / md.Hm)) : 0;
   const int ms = t * ROWS;
@@ -164,6 +168,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (warp == 9) {
     tmem_alloc(sbase + Cfg::OFF_MISC, 512);
     tmem_relinquish();
+    if (lane == 0) FPROF(12);
   }
   if (warp == 10) {
     // surviving K tiles, right to left, with the flags of both sub-tiles
@@ -171,6 +176,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // the reductions the classification needs are staged in the (still idle) K/V ring
     const MaskDesc mst = stage_minmax(md, bh_mask, 0, n_hi, reinterpret_cast<int32_t*>(smem + Cfg::OFF_STAGE),
                                       Cfg::LIST_MAX, lane);
+    if (lane == 0) FPROF(9);                 // reductions staged
     for (int base = n_hi - 1; base >= 0; base -= 32) {
       const int n = base - lane;
       uint32_t f0 = 0, f1 = 0;
@@ -193,7 +199,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       c0 += __popc(__ballot_sync(0xffffffffu, f0 != 0));
       c1 += __popc(__ballot_sync(0xffffffffu, f1 != 0));
     }
-    if (lane == 0) { misc[1] = min(cnt, Cfg::LIST_MAX); misc[2] = c0; misc[3] = c1; }
+    if (lane == 0) { misc[1] = min(cnt, Cfg::LIST_MAX); misc[2] = c0; misc[3] = c1; FPROF(10); }
     fence_proxy_async_smem();   // the staging area is handed back to the TMA loads of the ring
   }
   tc_fence_before();
@@ -521,7 +527,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 // ---------------------------------------------------------------------------
 #ifdef FM_TRACE
 extern "C" __attribute__((visibility("default"))) int fm_debug_fprof_read(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_fprof, sizeof(long long) * 64 * 8);
+  return (int)cudaMemcpyFromSymbol(out, g_fprof, sizeof(long long) * 64 * 16);
 }
 #endif
 
