@@ -154,6 +154,17 @@ def test_masks_d192(kind):
     assert _kernel_status() == 0
 
 
+@pytest.mark.parametrize("d,dv", [(192, 128), (256, 256)])
+@pytest.mark.parametrize("kind", ["causal_doc", "none_causal", "bidir_doc"])
+def test_ragged_shapes_big_head_dims(kind, d, dv):
+    """Sq != Sk and lengths that are no multiple of any tile through the 192 / 128 and 256 / 256 variants."""
+    _run(kind, 1, 300, 300, 2, 2, d, dv, seed=61)
+    if kind != "bidir_doc":
+        _run(kind, 1, 203, 333, 2, 1, d, dv, sink=True, seed=62)
+        _run(kind, 2, 333, 203, 4, 2, d, dv, seed=63)
+    assert _kernel_status() == 0
+
+
 @pytest.mark.parametrize("kind", MASKS)
 def test_masks_d256(kind):
     """Every mask family through the 256 / 256 forward variant of the tcgen05 kernel (128 query rows per CTA, the
