@@ -355,6 +355,9 @@ def make_workload(name: str, S: Optional[int] = None) -> Workload:
         hq, hkv, d, dv = shapes[kind]
         return Workload(name, 1, S, S, hq, hkv, d, dv, None, True, sink=True,
                         deterministic=True, seed=3)
+    if name in ("dense8k_full_gqa", "dense8k_causal_gqa"):     # no mask tensor: the dense points of the headline shape
+        S = S or 8192
+        return Workload(name, 2, S, S, 32, 8, 128, 128, None, name == "dense8k_causal_gqa", seed=5)
     if name == "cp_causal_doc_128k":
         S = S or 131072
         rng = np.random.default_rng(4)
@@ -371,5 +374,6 @@ WORKLOADS = [
     "sweep32k_sliding_window", "sweep32k_causal_doc", "sweep32k_share_question",
     "sweep32k_bidir_doc", "sweep32k_random_eviction",
     "bigd16k_192_128", "bigd16k_576_512", "bigd16k_256_256",
+    "dense8k_full_gqa", "dense8k_causal_gqa",
     "cp_causal_doc_128k",
 ]
