@@ -38,17 +38,58 @@ UNIT = "TFLOP/s"
 # clocks
 # ---------------------------------------------------------------------------
 class ClockSampler:
-    """Samples SM clocks / throttle reasons with nvidia-smi while running."""
+    """Samples SM clocks / throttle reasons while running: NVML polled every few ms from a thread (read-only
+    queries), or `nvidia-smi -lms 100` when the NVML binding is not importable."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    # bits of the NVML clocks-event (throttle) reasons word
+    BITS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
     def __init__(self, index: int):
         self.index = index
         self.samples = []
         self.proc = None
+        self.nv = None
+        self._stop = False
+
+    def _start_nvml(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            uuid = "GPU-" + str(torch.cuda.get_device_properties(self.index).uuid)
+            try:
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+        except Exception:
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+        self.reasons_fn = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+        self.mx = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        pynvml.nvmlDeviceGetClockInfo(self.h, pynvml.NVML_CLOCK_SM)       # fails here rather than in the thread
+        self.nv = pynvml
+        self.thread = threading.Thread(target=self._poll, daemon=True)
+        self.thread.start()
+
+    def _poll(self):
+        nv = self.nv
+        while not self._stop:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                word = int(self.reasons_fn(self.h))
+                f = [str(mhz), str(self.mx)] + ["Active" if word & bit else "Not Active" for _, bit in self.BITS]
+                self.samples.append((time.perf_counter(), ", ".join(f)))
+            except Exception:
+                pass
+            time.sleep(0.004)
 
     def start(self):
+        try:
+            self._start_nvml()
+            return
+        except Exception:
+            self.nv = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
@@ -68,17 +109,21 @@ class ClockSampler:
         self.t_mark = time.perf_counter()
 
     def stop(self):
-        if self.proc is None:
+        if self.proc is None and self.nv is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         t_end = time.perf_counter()
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=2)
-        except Exception:
-            pass
+        if self.nv is not None:
+            self._stop = True
+            self.thread.join(timeout=1)
+        else:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                pass
         t_mark = getattr(self, "t_mark", 0.0)
-        inside = [l for t, l in self.samples if t_mark <= t <= t_end + 0.1]
+        inside = [l for t, l in self.samples if t_mark <= t <= t_end + (0.0 if self.nv is not None else 0.1)]
         window = "timed region"
         if not inside:      # a timed region shorter than the sampling period: the warm-up ran the same load
             inside, window = [l for _, l in self.samples], "warm-up + timed region"
@@ -97,7 +142,7 @@ class ClockSampler:
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None,
                 "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm),
-                "window": window}
+                "window": window, "source": "nvml" if self.nv is not None else "nvidia-smi"}
 
 
 # ---------------------------------------------------------------------------
