@@ -433,9 +433,14 @@ bwd_sm100_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
           // the accumulators already hold S - LSE/scale and dP - rowsum(O dO) (statistics k-step)
           float pe[16], de[16];
 #pragma unroll
-          for (int c = 0; c < 16; ++c) pe[c] = fast_exp2(__uint_as_float(sr[hc][c0 + c]) * scale_log2);
+          for (int c = 0; c < 16; c += 2) {
+            float x0, x1;
+            mul2(x0, x1, __uint_as_float(sr[hc][c0 + c]), __uint_as_float(sr[hc][c0 + c + 1]), scale_log2, scale_log2);
+            pe[c] = fast_exp2(x0); pe[c + 1] = fast_exp2(x1);
+          }
 #pragma unroll
-          for (int c = 0; c < 16; ++c) de[c] = pe[c] * __uint_as_float(dr[hc][c0 + c]);
+          for (int c = 0; c < 16; c += 2)
+            mul2(de[c], de[c + 1], pe[c], pe[c + 1], __uint_as_float(dr[hc][c0 + c]), __uint_as_float(dr[hc][c0 + c + 1]));
           uint32_t pk1[8], pk2[8];
 #pragma unroll
           for (int c = 0; c < 8; ++c) {

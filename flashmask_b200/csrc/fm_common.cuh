@@ -265,6 +265,30 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Two fp32 lanes per instruction (sm_100 packed arithmetic): (x0, x1) = (a0, a1) * b + c and (a0, a1) += (b0, b1).
+// They halve the issue slots the softmax spends on scaling the scores and on the row sums.
+__device__ __forceinline__ void fma2_scalar(float& x0, float& x1, float a0, float a1, float b, float c) {
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(x0), "=f"(x1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void mul2(float& x0, float& x1, float a0, float a1, float b0, float b1) {
+  asm("{\n\t.reg .b64 ra, rb;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 ra, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, ra;\n\t}"
+      : "=f"(x0), "=f"(x1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ void add2(float& a0, float& a1, float b0, float b1) {
+  asm("{\n\t.reg .b64 ra, rb;\n\t"
+      "mov.b64 ra, {%0, %1};\n\tmov.b64 rb, {%2, %3};\n\t"
+      "add.rn.f32x2 ra, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, ra;\n\t}"
+      : "+f"(a0), "+f"(a1) : "f"(b0), "f"(b1));
+}
+
 // Byte offset of 16-byte chunk `chunk` of row `row` in a tile whose rows hold
 // ROW_BYTES bytes (ROW_BYTES/16 a multiple of 8): XOR swizzle on the low 3 bits
 // so that ldmatrix over 8 consecutive rows is bank-conflict free.
