@@ -274,6 +274,12 @@ __device__ __forceinline__ void fma2_scalar(float& x0, float& x1, float a0, floa
       "mov.b64 {%0, %1}, rd;\n\t}"
       : "=f"(x0), "=f"(x1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
 }
+// max(a, b, c) in one instruction (sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
 __device__ __forceinline__ void mul2(float& x0, float& x1, float a0, float a1, float b0, float b1) {
   asm("{\n\t.reg .b64 ra, rb;\n\t"
       "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
