@@ -493,10 +493,22 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         for (int i = 0; i < cnt && ok; ++i) {
           const uint32_t e = list[i];
           const uint32_t en = (i + 1 < cnt) ? list[i + 1] : 0u;
-          if ((e >> 16) & 0xFu) issue_pv(std::integral_constant<int, 0>{}, i);
-          if (ok && ((en >> 16) & 0xFu)) issue_qk(std::integral_constant<int, 0>{}, i + 1);
-          if (ok && ((e >> 20) & 0xFu)) issue_pv(std::integral_constant<int, 1>{}, i);
-          if (ok && ((en >> 20) & 0xFu)) issue_qk(std::integral_constant<int, 1>{}, i + 1);
+          // the sub-tile whose P is ready first goes first (sub-tile 0 when both or neither are)
+          bool one_first = false;
+          if (((e >> 16) & 0xFu) && ((e >> 20) & 0xFu))
+            one_first = !mbar_try_wait(bar(Cfg::B_PFULL + 0), (uint32_t)npv[0] & 1u) &&
+                        mbar_try_wait(bar(Cfg::B_PFULL + 1), (uint32_t)npv[1] & 1u);
+          if (one_first) {
+            issue_pv(std::integral_constant<int, 1>{}, i);
+            if (ok && ((en >> 20) & 0xFu)) issue_qk(std::integral_constant<int, 1>{}, i + 1);
+            if (ok) issue_pv(std::integral_constant<int, 0>{}, i);
+            if (ok && ((en >> 16) & 0xFu)) issue_qk(std::integral_constant<int, 0>{}, i + 1);
+          } else {
+            if ((e >> 16) & 0xFu) issue_pv(std::integral_constant<int, 0>{}, i);
+            if (ok && ((en >> 16) & 0xFu)) issue_qk(std::integral_constant<int, 0>{}, i + 1);
+            if (ok && ((e >> 20) & 0xFu)) issue_pv(std::integral_constant<int, 1>{}, i);
+            if (ok && ((en >> 20) & 0xFu)) issue_qk(std::integral_constant<int, 1>{}, i + 1);
+          }
           if (!ok) break;
           tc_commit(bar(Cfg::B_KVEMPTY + (2 * i + 1) % Cfg::NSTAGE));
           if (i + 1 < cnt) tc_commit(bar(Cfg::B_KVEMPTY + (2 * i + 2) % Cfg::NSTAGE));
